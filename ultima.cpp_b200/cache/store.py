@@ -45,8 +45,9 @@ class KVView:
 @dataclass
 class RunCache:
     kv: Optional[KVView] = None
-    state: Optional[torch.Tensor] = None     # [slots, ...]; rows are slot numbers
+    state: Optional[torch.Tensor] = None     # [slots, ...]; rows are slot numbers (the first of ``states``)
     owner: bool = True
+    states: tuple = ()                       # one array for each StateNeed the run named, in that order
 
 
 class KVGroup:
@@ -59,7 +60,7 @@ class KVGroup:
         self.pages_of = [[] for _ in range(n_slots)]
         shape = (len(self.runs), n_pages, need.n_kv_heads, PAGE, need.head_dim)
         self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape, dtype=dtype, device=device)
+        self.v = torch.empty(shape[:-1] + (need.v_head_dim or need.head_dim,), dtype=dtype, device=device)
         if poison:
             self.k.fill_(float("nan"))
             self.v.fill_(float("nan"))
@@ -72,7 +73,7 @@ class KVGroup:
         return self.ring_pages * PAGE
 
     def nbytes(self) -> int:
-        return 2 * self.k.numel() * self.k.element_size()
+        return (self.k.numel() + self.v.numel()) * self.k.element_size()
 
 
 class StateGroup:
@@ -101,12 +102,13 @@ class Cache:
         self.kv_groups: list[KVGroup] = []
         self.state_groups: list[StateGroup] = []
         self._kv_of_run: dict[int, KVGroup] = {}
-        self._state_of_run: dict[int, StateGroup] = {}
+        self._state_of_run: dict[int, list] = {}             # run -> its StateGroups, in the order of its need
         self.cache_from = list(cache_from)
         total_pages = _ceil_div(self.max_tokens, PAGE)
         ctx_pages = _ceil_div(self.max_context, PAGE)
         kv_runs: dict[KVNeed, list] = {}
         st_runs: dict[StateNeed, list] = {}
+        st_order: dict[int, list] = {}
         for r, need in enumerate(needs):
             if self.cache_from[r] is not None:
                 src = self.cache_from[r]
@@ -118,7 +120,10 @@ class Cache:
                 if isinstance(n, KVNeed):
                     kv_runs.setdefault(n, []).append(r)
                 elif isinstance(n, StateNeed):
+                    if n in st_order.setdefault(r, []):
+                        raise CacheError(f"run {r} names the same state twice: {n!r}")
                     st_runs.setdefault(n, []).append(r)
+                    st_order[r].append(n)
                 elif n is not None:
                     raise CacheError(f"run {r}: unknown cache need {n!r}")
         for need, runs in kv_runs.items():
@@ -131,11 +136,12 @@ class Cache:
             self.kv_groups.append(g)
             for r in runs:
                 self._kv_of_run[r] = g
+        by_need = {}
         for need, runs in st_runs.items():
-            g = StateGroup(need, runs, self.n_slots, device)
+            g = by_need[need] = StateGroup(need, runs, self.n_slots, device)
             self.state_groups.append(g)
-            for r in runs:
-                self._state_of_run[r] = g
+        for r, ns in st_order.items():
+            self._state_of_run[r] = [by_need[n] for n in ns]
 
     # ---- slots ---------------------------------------------------------------------------
     def acquire(self) -> int:
@@ -223,9 +229,10 @@ class Cache:
             i = g.index[r]
             out.kv = KVView(g.k[i], g.v[i], tables_dev[self.kv_groups.index(g)], g.ring, PAGE,
                             g.need.window, owner)
-        sg = self._state_of_run.get(r)
-        if sg is not None:
-            out.state = sg.data[sg.index[r]]
+        sgs = self._state_of_run.get(r)
+        if sgs:
+            out.states = tuple(sg.data[sg.index[r]] for sg in sgs)
+            out.state = out.states[0]
         return out
 
     def nbytes(self) -> int:

@@ -113,9 +113,11 @@ def architecture_name(data: dict) -> str:
     archs = data.get("architectures")
     if isinstance(archs, list) and archs:
         return str(archs[0])
+    if isinstance(data.get("architecture"), str):
+        return data["architecture"]
     if "model_type" in data:
         return str(data["model_type"])
-    raise ConfigError("config.json names no architecture (neither 'architectures' nor 'model_type')")
+    raise ConfigError("config.json names no architecture (none of 'architectures', 'architecture', 'model_type')")
 
 
 def config_from_dict(data: dict):
@@ -151,4 +153,24 @@ def config_from_dir(model_dir: str):
                 if v not in ids:
                     ids.append(v)
             data = dict(data, eos_token_id=ids)
-    return config_from_dict(data)
+    cfg = config_from_dict(data)
+    # a design may leave sizes to the stored tensors' shapes; its configuration then asks for them
+    if getattr(cfg, "needs_tensor_shapes", False):
+        cfg = cfg.with_tensor_shapes(_tensor_shapes(model_dir))
+    return cfg
+
+
+def _tensor_shapes(model_dir: str) -> dict:
+    """Stored name -> shape of every tensor in the folder's safetensors files (headers only)."""
+    from ..weights.loader import _shard_files
+    from ..weights.safetensors_io import read_safetensors_header
+    shapes = {}
+    try:
+        files = _shard_files(model_dir)
+    except ValueError:
+        return shapes
+    for path in files:
+        header, _, _ = read_safetensors_header(path)
+        for n, e in header.items():
+            shapes[n] = tuple(int(x) for x in e["shape"])
+    return shapes

@@ -7,6 +7,13 @@
 // p sees positions (p - window, p] (src/model/qwen_block.cpp:742-745).  Keys are taken in
 // chunks with a running maximum, so the context length is not bounded by shared memory.
 // The order of every sum depends only on the key range, never on the batch.
+//
+// Beyond the reference: values may have a head size of their own (``hd_v``); ``block`` > 0 masks by
+// blocks of positions counted from the sequence's start (p sees j <= p with j / block == p / block);
+// ``gate`` (float32, one number a token and head) multiplies a head's output by its sigmoid.  The
+// placement kernel at the end prepares queries and fills the cache from projection rows whose q, k and
+// v columns lie anywhere, for layers the fused preparation of basic.cu does not take (unequal head
+// sizes, no keys and values of their own).
 #include "common.cuh"
 
 constexpr int CHUNK = 512;
@@ -15,18 +22,19 @@ template <typename TQ, typename TC>
 __global__ void __launch_bounds__(128)
 attn_simple_kernel(const TQ* __restrict__ q, long long q_stride, const TC* __restrict__ kc,
                    const TC* __restrict__ vc, TQ* __restrict__ out, long long o_stride,
-                   const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, PagedKV c,
-                   int nh, int window, float scale) {
+                   const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, PagedKV c, PagedKV cv,
+                   int nh, int window, int block, const float* __restrict__ gate, long long g_stride, float scale) {
     extern __shared__ float smem[];
     float* qs = smem;                    // [hd]
     float* sc = smem + c.head_dim;       // [CHUNK]
     __shared__ float red[33];
     const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-    const int hd = c.head_dim;
+    const int hd = c.head_dim, hdv = cv.head_dim;
     const int kvh = h / (nh / c.n_kv_heads);
     const int pos = tok_pos[t], seq = tok_seq[t];
     int lo = 0;
     if (window > 0 && pos + 1 > window) lo = pos + 1 - window;
+    if (block > 0) lo = max(lo, pos - pos % block);
     for (int i = tid; i < hd; i += blockDim.x) qs[i] = to_f32<TQ>(q[(long long)t * q_stride + (long long)h * hd + i]);
     __syncthreads();
     float m = -INFINITY, l = 0.f, acc0 = 0.f, acc1 = 0.f;
@@ -56,17 +64,18 @@ attn_simple_kernel(const TQ* __restrict__ q, long long q_stride, const TC* __res
         acc0 *= corr;
         acc1 *= corr;
         for (int j = 0; j < n; ++j) {
-            const TC* vr = vc + paged_offset(c, seq, c0 + j, kvh);
+            const TC* vr = vc + paged_offset(cv, seq, c0 + j, kvh);
             const float p = sc[j];
-            if (tid < hd) acc0 = fmaf(p, to_f32<TC>(vr[tid]), acc0);
-            if (tid + 128 < hd) acc1 = fmaf(p, to_f32<TC>(vr[tid + 128]), acc1);
+            if (tid < hdv) acc0 = fmaf(p, to_f32<TC>(vr[tid]), acc0);
+            if (tid + 128 < hdv) acc1 = fmaf(p, to_f32<TC>(vr[tid + 128]), acc1);
         }
         __syncthreads();
     }
-    const float inv = 1.0f / l;
-    TQ* o = out + (long long)t * o_stride + (long long)h * hd;
-    if (tid < hd) o[tid] = from_f32<TQ>(acc0 * inv);
-    if (tid + 128 < hd) o[tid + 128] = from_f32<TQ>(acc1 * inv);
+    float inv = 1.0f / l;
+    if (gate) inv *= 1.0f / (1.0f + expf(-gate[(long long)t * g_stride + h]));
+    TQ* o = out + (long long)t * o_stride + (long long)h * hdv;
+    if (tid < hdv) o[tid] = from_f32<TQ>(acc0 * inv);
+    if (tid + 128 < hdv) o[tid + 128] = from_f32<TQ>(acc1 * inv);
 }
 
 // q: [T, *] with row stride q_stride (elements), heads side by side; out likewise.
@@ -74,14 +83,16 @@ UB_API int ub_attn_simple(const void* q, long long q_stride, int act_dtype, cons
                           const void* vcache, int cache_dtype, void* out, long long o_stride,
                           const int* tok_pos, const int* tok_seq, const int* table, int pages_per_seq,
                           int ring, int page, int n_tokens, int nh, int nkv, int hd, int window,
-                          float scale, cudaStream_t st) {
+                          float scale, int hd_v, int block, const float* gate, long long g_stride, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    if (hd > 256 || hd <= 0 || nh % nkv != 0 || ring % page != 0 || nh > 65535) return UB_ERR_ARG;
+    if (hd_v <= 0) hd_v = hd;
+    if (hd > 256 || hd <= 0 || hd_v > 256 || nh % nkv != 0 || ring % page != 0 || nh > 65535 || block < 0) return UB_ERR_ARG;
     PagedKV c{table, pages_per_seq, ring, page, nkv, hd};
+    PagedKV cv{table, pages_per_seq, ring, page, nkv, hd_v};
     dim3 grid(n_tokens, nh);
     const size_t sm = (size_t)(hd + CHUNK) * sizeof(float);
 #define GO(TQ, TC) attn_simple_kernel<TQ, TC><<<grid, 128, sm, st>>>((const TQ*)q, q_stride, (const TC*)kcache, \
-        (const TC*)vcache, (TQ*)out, o_stride, tok_pos, tok_seq, c, nh, window, scale)
+        (const TC*)vcache, (TQ*)out, o_stride, tok_pos, tok_seq, c, cv, nh, window, block, gate, g_stride, scale)
     if (act_dtype == UB_F32 && cache_dtype == UB_F32) GO(float, float);
     else if (act_dtype == UB_BF16 && cache_dtype == UB_BF16) GO(__nv_bfloat16, __nv_bfloat16);
     else if (act_dtype == UB_F32 && cache_dtype == UB_BF16) GO(float, __nv_bfloat16);
@@ -89,4 +100,111 @@ UB_API int ub_attn_simple(const void* q, long long q_stride, int act_dtype, cons
 #undef GO
     UB_LAUNCH_CHECK();
     return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Placement: from projection rows ``x`` (row stride ldx; the sum of ``n_parts`` parts ``part_stride`` apart) whose
+// query heads start at column q_off, key heads at k_off and value heads at v_off, make
+//   q_out[t, h, :]   = rotate(norm(q))      activation type, row stride ldq
+//   K cache          = rotate(norm(k))      at the token's position
+//   V cache          = v                    (head size hd_v)
+// norm: RMS over the head with weight qw / kw (null: none); rotate: the first ``rd`` columns in pairs
+// (j, j + rd/2) by the token's position (cos, sin [positions, rd/2]; null: none).  k_off < 0: the layer
+// has no keys and values of its own and only its queries are made.  One warp a (token, head).
+// ---------------------------------------------------------------------------------------
+template <typename TX, typename TQ, typename TC>
+__global__ void __launch_bounds__(128)
+qkv_place_kernel(const TX* __restrict__ x, long long ldx, int n_parts, long long part_stride, int q_off, int k_off, int v_off,
+                 TQ* __restrict__ q_out, long long ldq, const float* __restrict__ qw, const float* __restrict__ kw,
+                 const float* __restrict__ cs, const float* __restrict__ sn, int rd, const int* __restrict__ tok_pos,
+                 const int* __restrict__ tok_seq, TC* __restrict__ kc, TC* __restrict__ vc, PagedKV c, PagedKV cv,
+                 int n_tokens, int nh, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int units = nh + (k_off >= 0 ? 2 * c.n_kv_heads : 0);
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)n_tokens * units) return;
+    const long long t = wid / units;
+    const int unit = (int)(wid % units);
+    const int pos = tok_pos[t], seq = tok_seq[t];
+    auto at = [&](int col) -> float {
+        float v = 0.f;
+        for (int p = 0; p < n_parts; ++p) v += to_f32<TX>(x[p * part_stride + t * ldx + col]);
+        return v;
+    };
+    if (unit >= nh + c.n_kv_heads) {                       // a value head: copied as it is
+        const int g = unit - nh - c.n_kv_heads;
+        TC* dst = vc + paged_offset(cv, seq, pos, g);
+        for (int e = lane; e < cv.head_dim; e += 32) dst[e] = from_f32<TC>(at(v_off + g * cv.head_dim + e));
+        return;
+    }
+    const bool is_q = unit < nh;
+    const int head = is_q ? unit : unit - nh;
+    const int hd = c.head_dim;
+    const int c0 = (is_q ? q_off : k_off) + head * hd;
+    const float* w = is_q ? qw : kw;
+    float v[8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int d = lane + 32 * i;
+        v[i] = d < hd ? at(c0 + d) : 0.f;
+        ss += v[i] * v[i];
+    }
+    if (w) {
+        ss = warp_sum(ss);
+        const float inv = inv_rms(ss, (float)hd, eps);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d = lane + 32 * i;
+            if (d < hd) v[i] *= inv * w[d];
+        }
+    }
+    // the head goes through shared memory so that a lane can reach its rotation partner
+    __shared__ float sh[4][256];
+    float* my = sh[threadIdx.x >> 5];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int d = lane + 32 * i;
+        if (d < hd) my[d] = v[i];
+    }
+    __syncwarp();
+    const int half = rd >> 1;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int d = lane + 32 * i;
+        if (d >= hd) continue;
+        float o = v[i];
+        if (cs && d < rd) {
+            const int j = d < half ? d : d - half;
+            const float cj = cs[(long long)pos * half + j], sj = sn[(long long)pos * half + j];
+            o = d < half ? my[d] * cj - my[d + half] * sj : my[d] * cj + my[d - half] * sj;
+        }
+        if (is_q) q_out[t * ldq + (long long)head * hd + d] = from_f32<TQ>(o);
+        else kc[paged_offset(c, seq, pos, head) + d] = from_f32<TC>(o);
+    }
+}
+
+UB_API int ub_qkv_place(const void* x, int x_dtype, long long ldx, int n_parts, long long part_stride, int q_off, int k_off,
+                        int v_off, void* q_out, int q_dtype, long long ldq, const float* qw, const float* kw, const float* cs,
+                        const float* sn, int rd, const int* tok_pos, const int* tok_seq, void* kcache, void* vcache,
+                        int cache_dtype, const int* table, int pages_per_seq, int ring, int page, int n_tokens, int nh,
+                        int nkv, int hd, int hd_v, float eps, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (hd <= 0 || hd > 256 || hd_v <= 0 || nh <= 0 || nkv <= 0 || n_parts < 1 || (cs && (rd % 2 || rd < 2 || rd > hd)) ||
+        ring % page != 0) return UB_ERR_ARG;
+    PagedKV c{table, pages_per_seq, ring, page, nkv, hd};
+    PagedKV cv{table, pages_per_seq, ring, page, nkv, hd_v};
+    const long long warps = (long long)n_tokens * (nh + (k_off >= 0 ? 2 * nkv : 0));
+    const unsigned grid = (unsigned)((warps + 3) / 4);
+    cudaError_t e;
+#define GO(TX, TQ, TC) e = ub_launch_dependent(qkv_place_kernel<TX, TQ, TC>, dim3(grid), dim3(128), 0, st, (const TX*)x, ldx, n_parts, \
+        part_stride, q_off, k_off, v_off, (TQ*)q_out, ldq, qw, kw, cs, sn, rd, tok_pos, tok_seq, (TC*)kcache, (TC*)vcache, c, cv, n_tokens, nh, eps)
+    if (x_dtype == UB_F32 && q_dtype == UB_F32 && cache_dtype == UB_F32) GO(float, float, float);
+    else if (x_dtype == UB_F32 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) GO(float, __nv_bfloat16, __nv_bfloat16);
+    else if (x_dtype == UB_BF16 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    else return UB_ERR_UNSUPPORTED;
+#undef GO
+    return (int)e;
 }

@@ -477,6 +477,108 @@ UB_API int ub_qk_prepare(const void* qkv, int in_dtype, int n_parts, long long p
 }
 
 // ---------------------------------------------------------------------------------------
+// The norm on a sublayer's output: x[r, :] += y[r, :] * w / sqrt(mean(y[r, :]^2) + eps), x and y
+// float32.  In the same pass the kernel can hand the next sublayer its input (``h`` = the new x in the
+// activation type) and clear y, which sublayers add their output into.
+// ---------------------------------------------------------------------------------------
+template <typename TH>
+__global__ void rmsnorm_add_kernel(float* __restrict__ y, const float* __restrict__ w, float* __restrict__ x,
+                                   TH* __restrict__ h, int width, float eps, int clear_y) {
+    __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
+    const long long r = blockIdx.x;
+    float* yr = y + r * width;
+    float* xr = x + r * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) { const float v = yr[i]; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float inv = inv_rms(ss, (float)width, eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = xr[i] + yr[i] * w[i] * inv;
+        xr[i] = v;
+        if (h) h[r * width + i] = from_f32<TH>(v);
+        if (clear_y) yr[i] = 0.f;
+    }
+}
+
+UB_API int ub_rmsnorm_add(float* y, const float* w, float* x, void* h, int h_dtype, int n_rows, int width,
+                          float eps, int clear_y, cudaStream_t st) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    cudaError_t e;
+    if (h == nullptr || h_dtype == UB_F32)
+        e = ub_launch_dependent(rmsnorm_add_kernel<float>, dim3(n_rows), dim3(threads), 0, st, y, w, x, (float*)h, width, eps, clear_y);
+    else if (h_dtype == UB_BF16)
+        e = ub_launch_dependent(rmsnorm_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, st, y, w, x, (__nv_bfloat16*)h, width, eps, clear_y);
+    else return UB_ERR_UNSUPPORTED;
+    return (int)e;
+}
+
+// ---------------------------------------------------------------------------------------
+// The clamped gate product: with g' = min(g, limit) and u' = clamp(u, -limit, limit),
+// out[t, f] = g' * sigmoid(alpha * g') * (u' + shift); gate and up side by side in one row of gu.
+// ---------------------------------------------------------------------------------------
+template <typename TI, typename TO>
+__global__ void glu_clamped_kernel(const TI* __restrict__ gu, TO* __restrict__ out, long long n, int F,
+                                   float limit, float alpha, float shift) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / F;
+    const int f = (int)(i % F);
+    const float g = fminf(to_f32<TI>(gu[t * 2 * F + f]), limit);
+    const float u = fminf(fmaxf(to_f32<TI>(gu[t * 2 * F + F + f]), -limit), limit);
+    out[i] = from_f32<TO>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+}
+
+UB_API int ub_glu_clamped(const void* gu, int in_dtype, void* out, int out_dtype, int n_tokens, int F,
+                          float limit, float alpha, float shift, cudaStream_t st) {
+    const long long n = (long long)n_tokens * F;
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned)((n + 255) / 256);
+    cudaError_t e;
+#define LAUNCH(TI, TO) e = ub_launch_dependent(glu_clamped_kernel<TI, TO>, dim3(grid), dim3(256), 0, st, (const TI*)gu, (TO*)out, n, F, limit, alpha, shift)
+    if (in_dtype == UB_F32 && out_dtype == UB_F32) LAUNCH(float, float);
+    else if (in_dtype == UB_F32 && out_dtype == UB_BF16) LAUNCH(float, __nv_bfloat16);
+    else if (in_dtype == UB_BF16 && out_dtype == UB_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+    else return UB_ERR_UNSUPPORTED;
+#undef LAUNCH
+    return (int)e;
+}
+
+// ---------------------------------------------------------------------------------------
+// One gate a head: o[t, h, :] *= sigmoid(g[t * g_stride + h]), g float32 (a column range of a wider row).
+// ---------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void head_gate_kernel(TO* __restrict__ o, long long o_stride, const float* __restrict__ g, long long g_stride,
+                                 long long n, int n_heads, int hd) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int per = n_heads * hd;
+    const long long t = i / per;
+    const int c = (int)(i % per);
+    const float s = 1.0f / (1.0f + expf(-g[t * g_stride + c / hd]));
+    TO* p = o + t * o_stride + c;
+    *p = from_f32<TO>(to_f32<TO>(*p) * s);
+}
+
+UB_API int ub_head_gate(void* o, int o_dtype, long long o_stride, const float* g, long long g_stride, int n_tokens,
+                        int n_heads, int hd, cudaStream_t st) {
+    const long long n = (long long)n_tokens * n_heads * hd;
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned)((n + 255) / 256);
+    cudaError_t e;
+    if (o_dtype == UB_F32) e = ub_launch_dependent(head_gate_kernel<float>, dim3(grid), dim3(256), 0, st, (float*)o, o_stride, g, g_stride, n, n_heads, hd);
+    else if (o_dtype == UB_BF16) e = ub_launch_dependent(head_gate_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (__nv_bfloat16*)o, o_stride, g, g_stride, n, n_heads, hd);
+    else return UB_ERR_UNSUPPORTED;
+    return (int)e;
+}
+
+// ---------------------------------------------------------------------------------------
 // out[t, f] = silu(gu[t, f]) * gu[t, F + f]   (gate and up side by side in one row)
 // ---------------------------------------------------------------------------------------
 template <typename TI, typename TO>

@@ -49,7 +49,7 @@ class Model:
 
         def bound(family, ps, prefix):
             p = build_part(family, ps)
-            p.bind({s.name: tensors[prefix + s.name] for s in p.weight_specs()}, rt)
+            p.bind({s.name: tensors[spec.stored_name(prefix + s.name)] for s in p.weight_specs()}, rt)
             return p
 
         self.embedding = bound("embedding", spec.embedding, spec.embedding_name)
@@ -63,7 +63,8 @@ class Model:
         if spec.head.get("tied"):
             self.head.bind({"weight": self.embedding.table}, rt)
         else:
-            self.head.bind({s.name: tensors[spec.head_name + s.name] for s in self.head.weight_specs()}, rt)
+            self.head.bind({s.name: tensors[spec.stored_name(spec.head_name + s.name)]
+                            for s in self.head.weight_specs()}, rt)
         for r in spec.runs:
             if not (0 <= r.layer < len(self.layers)):
                 raise ValueError(f"run list names layer {r.layer}; the model has {len(self.layers)}")
@@ -93,6 +94,7 @@ class Model:
         extended in place."""
         rt = self.rt
         rt.arena.reset(0)
+        rt.pass_id += 1
         x = self.embedding.forward(batch.tok_ids, rt)
         if TRACE:
             _trace("embd", 0, x)

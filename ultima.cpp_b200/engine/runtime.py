@@ -85,6 +85,8 @@ class Runtime:
         self._shared: dict = {}
         self.use_tensor_cores = dtype == torch.bfloat16
         self.launches = 0              # kernels of this library launched through the runtime
+        self.pass_id = 0               # counts the passes through the layers (Model.forward); what an arrangement
+                                       # keeps from layer to layer is valid within one pass only
         # flags the kernels raise: [0] a token id outside the vocabulary, [1] a wait that ran out
         # (they are the head of a buffer whose tail takes the sampled token ids: one copy brings both)
         self.status_and_ids = torch.zeros(4 + 4096, dtype=torch.int32, device=self.device)
@@ -155,6 +157,18 @@ class Runtime:
         if done:
             self.launches += 1
         return done
+
+    def attention_fast(self, q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, block=None) -> bool:
+        """The tensor-core attention kernels with a block mask (``block`` positions, counted from the
+        sequence's start), where they take the case; False where they do not, and nothing was launched."""
+        if not (self.use_tensor_cores and q.dtype == torch.bfloat16):
+            return False
+        from ..kernels import attn_tc
+        if not attn_tc.accepts(q, kv, head_dim, n_heads, n_kv_heads) or not attn_tc.BLOCK_MASK:
+            return False
+        self.launches += 1
+        attn_tc.attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, self, block=block)
+        return True
 
     def attention(self, q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale):
         self.launches += 1

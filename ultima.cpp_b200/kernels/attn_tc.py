@@ -195,9 +195,23 @@ def decode_from_qkv(qkv, q_norm, k_norm, cos, sin, eps, kv, out, batch, n_heads,
     return True
 
 
+# The kernels take the mask as one integer: w > 0, the last w positions; w < 0, blocks of -w positions
+# counted from the sequence's start (a token sees the earlier tokens of its own block); 0, everything before.
+BLOCK_MASK = False
+
+
+def _mask_arg(kv, block) -> int:
+    if block:
+        if kv.window:
+            raise KernelError("attention: a window and a block mask together are not built into these kernels")
+        return -int(block)
+    return int(kv.window or 0)
+
+
 def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slices: int | None = None,
-              kernel: str | None = None):
-    """kernel: None picks (tcgen05 for prompts where it fits, mma.sync otherwise); "mma" forces the latter."""
+              kernel: str | None = None, block: int | None = None):
+    """kernel: None picks (tcgen05 for prompts where it fits, mma.sync otherwise); "mma" forces the latter.
+    ``block``: mask by blocks of this many positions instead of by the cache's window."""
     L = lib(head_dim)
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1
     group = n_heads // n_kv_heads

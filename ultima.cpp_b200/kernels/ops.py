@@ -103,12 +103,21 @@ def _declare(lib, source: str) -> None:
             "ub_rotate_pairs": [P, I, L, I, I, I, P, P, P, I, I, P],
             "ub_kv_write": [P, P, I, L, P, P, P, P, I, P, I, I, I, I, I, I, P],
             "ub_silu_mul": [P, I, I, L, P, I, I, I, P],
+            "ub_rmsnorm_add": [P, P, P, P, I, I, I, F, I, P],
+            "ub_glu_clamped": [P, I, P, I, I, I, F, F, F, P],
+            "ub_head_gate": [P, I, L, P, L, I, I, I, P],
             "ub_convert": [P, I, P, I, L, P],
             "ub_add_into": [P, P, I, L, P],
             "ub_fill_normal": [P, I, L, U, F, F, P],
         },
         "gemm_simt.cu": {"ub_gemm_simt": [P, I, P, P, I, P, I, I, I, I, L, L, L, I, P]},
-        "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, P]},
+        "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, L, P],
+                           "ub_qkv_place": [P, I, L, I, L, I, I, I, P, I, L, P, P, P, P, I, P, P, P, P, I, P, I, I, I, I, I,
+                                            I, I, I, F, P]},
+        "delta.cu": {"ub_delta_prepare": [P, L, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, F, F, P],
+                     "ub_conv_state_update": [P, L, P, P, P, I, I, I, P],
+                     "ub_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+                     "ub_delta_finish": [P, P, L, I, I, P, P, P, I, I, I, I, F, P]},
         "sampling.cu": {"ub_sample": [P, L, P, I, I, P, P, P, P, P, U, P, P, I, P], "ub_sample_params_size": []},
     }.get(source, {})
     for name, args in sigs.items():
@@ -230,6 +239,37 @@ def silu_mul(gate_up, out):
                                         _code(out), T, F, _stream()), "silu_mul")
 
 
+def rmsnorm_add(y, weight, x, eps, h=None, clear_y=False):
+    """x += y * weight / sqrt(mean(y^2) + eps), row by row (x, y float32).  ``h``: the new x in h's type,
+    for the next reader; ``clear_y``: y is zeroed behind the read."""
+    _need_cuda(y, weight, x, h)
+    n, width = x.shape
+    assert x.dtype == y.dtype == weight.dtype == torch.float32 and y.shape == x.shape and weight.numel() == width
+    assert x.is_contiguous() and y.is_contiguous() and (h is None or (h.is_contiguous() and h.shape == x.shape))
+    _check(_lib("basic.cu").ub_rmsnorm_add(_ptr(y), _ptr(weight), _ptr(x), _ptr(h), _code(h) if h is not None else F32,
+                                           n, width, float(eps), 1 if clear_y else 0, _stream()), "rmsnorm_add")
+
+
+def glu_clamped(gate_up, out, limit, alpha, shift):
+    """out = g' * sigmoid(alpha g') * (u' + shift) with g' = min(g, limit), u' = clamp(u, -limit, limit);
+    gate_up [T, 2F] holds g and u side by side."""
+    _need_cuda(gate_up, out)
+    T, F = out.shape
+    assert gate_up.shape == (T, 2 * F) and gate_up.is_contiguous() and out.is_contiguous()
+    _check(_lib("basic.cu").ub_glu_clamped(_ptr(gate_up), _code(gate_up), _ptr(out), _code(out), T, F, float(limit),
+                                           float(alpha), float(shift), _stream()), "glu_clamped")
+
+
+def head_gate(o, gate, n_heads, head_dim):
+    """o[t, h, :] *= sigmoid(gate[t, h]) in place; gate float32 [T, heads] (any row stride)."""
+    _need_cuda(o, gate)
+    T = o.shape[0]
+    assert o.stride(1) == 1 and o.shape[1] == n_heads * head_dim and gate.dtype == torch.float32
+    assert gate.shape == (T, n_heads) and gate.stride(1) == 1
+    _check(_lib("basic.cu").ub_head_gate(_ptr(o), _code(o), o.stride(0), _ptr(gate), gate.stride(0), T, n_heads, head_dim,
+                                         _stream()), "head_gate")
+
+
 def convert(src, dst):
     _need_cuda(src, dst)
     assert src.numel() == dst.numel() and src.is_contiguous() and dst.is_contiguous()
@@ -268,16 +308,91 @@ def gemm_simt(a, w, out, epilogue=EPI_STORE, w2=None):
 
 
 def attn_simple(q, k_cache, v_cache, out, tok_pos, tok_seq, table, ring, page, n_heads,
-                n_kv_heads, head_dim, window, scale):
-    """Attention of every token of the step over its sequence's cached keys and values."""
-    _need_cuda(q, k_cache, v_cache, out, table)
+                n_kv_heads, head_dim, window, scale, v_head_dim=None, block=None, gate=None):
+    """Attention of every token of the step over its sequence's cached keys and values.  ``v_head_dim``:
+    the values' head size where it differs; ``block``: positions are masked in blocks of this many,
+    counted from the sequence's start; ``gate`` float32 [T, heads]: a head's output times its sigmoid."""
+    _need_cuda(q, k_cache, v_cache, out, table, gate)
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype
     assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.shape == (T, n_heads) and gate.stride(1) == 1
     _check(_lib("attn_simple.cu").ub_attn_simple(
         _ptr(q), q.stride(0), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out),
         out.stride(0), _ptr(tok_pos), _ptr(tok_seq), _ptr(table), table.shape[1], ring, page, T,
-        n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), _stream()), "attn_simple")
+        n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), int(v_head_dim or head_dim), int(block or 0),
+        _ptr(gate), gate.stride(0) if gate is not None else 0, _stream()), "attn_simple")
+
+
+def qkv_place(x, q_off, k_off, v_off, q_out, q_weight, k_weight, cos, sin, rotary_dim, tok_pos, tok_seq, k_cache,
+              v_cache, table, ring, page, n_heads, n_kv_heads, head_dim, v_head_dim, eps):
+    """Queries normed and rotated into ``q_out`` [T, heads * head size]; keys (normed, rotated) and values into the
+    paged cache.  x: projection rows [T, N] or [parts, T, N] (summed), with the query heads from column q_off, the
+    key heads from k_off and the value heads from v_off; k_off None: queries only."""
+    _need_cuda(x, q_out, k_cache, v_cache, table)
+    if x.dim() == 3:
+        n_parts, T, part_stride, ldx = x.shape[0], x.shape[1], x.stride(0), x.stride(1)
+        assert x.stride(2) == 1
+    else:
+        n_parts, T, part_stride, ldx = 1, x.shape[0], 0, x.stride(0)
+        assert x.stride(1) == 1
+    assert q_out.stride(1) == 1 and q_out.shape == (T, n_heads * head_dim)
+    assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    for v in (q_weight, k_weight, cos, sin):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous())
+    rd = int(rotary_dim or 0)
+    if cos is not None:
+        assert cos.shape[1] == rd // 2 and sin.shape == cos.shape
+    _check(_lib("attn_simple.cu").ub_qkv_place(
+        _ptr(x), _code(x), ldx, n_parts, part_stride, int(q_off), -1 if k_off is None else int(k_off),
+        -1 if v_off is None else int(v_off), _ptr(q_out), _code(q_out), q_out.stride(0), _ptr(q_weight), _ptr(k_weight),
+        _ptr(cos), _ptr(sin), rd, _ptr(tok_pos), _ptr(tok_seq), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(table),
+        table.shape[1], ring, page, T, n_heads, n_kv_heads, head_dim, int(v_head_dim), float(eps), _stream()), "qkv_place")
+
+
+# ---------------------------------------------------------------------------------------
+# the gated delta-rule mixer (csrc/delta.cu)
+def delta_shape(H, G, D, E, taps, rank_a, rank_g, offs):
+    """The shape record the delta kernels read: sizes and the columns of a projection row
+    (offs = (q, k, v, b, a, g) first columns)."""
+    from ctypes import c_int as _ci
+    vals = [H, G, D, E, taps, rank_a, rank_g] + [int(o) for o in offs]
+    return (_ci * len(vals))(*vals)
+
+
+def delta_prepare(p, shape, conv_w, conv_state, a2, dt_bias, a_log, batch, qn, kn, vc, beta, dec, unit_eps, q_scale):
+    _need_cuda(p, conv_w, conv_state, a2, qn, kn, vc, beta, dec)
+    assert p.dtype == torch.float32 and p.stride(1) == 1
+    for t in (conv_w, conv_state, a2, dt_bias, a_log, qn, kn, vc, beta, dec):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    _check(_lib("delta.cu").ub_delta_prepare(
+        _ptr(p), p.stride(0), shape, _ptr(conv_w), _ptr(conv_state), _ptr(a2), _ptr(dt_bias), _ptr(a_log),
+        _ptr(batch.tok_seq), _ptr(batch.seq_start), _ptr(batch.seq_slot), _ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta),
+        _ptr(dec), p.shape[0], float(unit_eps), float(q_scale), _stream()), "delta_prepare")
+
+
+def conv_state_update(p, conv_state, batch, n_channels, taps):
+    _need_cuda(p, conv_state)
+    assert p.dtype == torch.float32 and conv_state.dtype == torch.float32 and conv_state.is_contiguous()
+    _check(_lib("delta.cu").ub_conv_state_update(_ptr(p), p.stride(0), _ptr(conv_state), _ptr(batch.seq_start),
+                                                 _ptr(batch.seq_slot), batch.n_seqs, n_channels, taps, _stream()),
+           "conv_state_update")
+
+
+def delta_scan(qn, kn, vc, beta, dec, out, state, batch, H, G, D, E):
+    _need_cuda(qn, kn, vc, beta, dec, out, state)
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, D, E)
+    _check(_lib("delta.cu").ub_delta_scan(_ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(dec), _ptr(out), _ptr(state),
+                                          _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seqs, H, G, D, E, _stream()),
+           "delta_scan")
+
+
+def delta_finish(o, p, g_off, rank_g, g2, weight, out, H, E, eps):
+    _need_cuda(o, p, g2, weight, out)
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and g2.dtype == torch.float32
+    _check(_lib("delta.cu").ub_delta_finish(_ptr(o), _ptr(p), p.stride(0), int(g_off), int(rank_g), _ptr(g2), _ptr(weight),
+                                            _ptr(out), _code(out), o.shape[0], H, E, float(eps), _stream()), "delta_finish")
 
 
 # ---------------------------------------------------------------------------------------

@@ -22,6 +22,18 @@ class Attention(Mixer):
     :775-783, :94-135.
 
     The three projections are held as one matrix [q | k | v] and run as one product.
+
+    Further parameters, each off by default:
+      v_head_dim  the values' head size where it is not the keys'
+      block       a token at position p sees j <= p only with j // block == p // block (blocks are
+                  counted from the sequence's start, whatever a step brings)
+      head_gate   one more projection of the mixer's input, one number a head; a head's output is
+                  multiplied by its sigmoid before the output projection
+      own_kv      False: the layer has no key and value tensors; its run reads another run's cache
+                  (``Run.cache_from``) with its own queries
+    With any of them the layer runs on the general kernels (csrc/attn_simple.cu: placement of q, k, v from
+    one fused projection row [q | k | v | gate], attention with the mask and the gate inside); a block
+    mask alone, with equal head sizes, still takes the tensor-core attention kernels.
     """
 
     @property
@@ -32,7 +44,8 @@ class Attention(Mixer):
 
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, qk_norm: bool,
                  eps: float, position: PartSpec | None, window: int | None = None,
-                 scale: float | None = None):
+                 scale: float | None = None, v_head_dim: int | None = None, block: int | None = None,
+                 head_gate: bool = False, own_kv: bool = True):
         if n_heads % n_kv_heads:
             raise ValueError("heads must be a multiple of kv heads")
         self.width, self.nh, self.nkv, self.hd = int(width), int(n_heads), int(n_kv_heads), int(head_dim)
@@ -40,25 +53,43 @@ class Attention(Mixer):
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.hd)
         self.position = build_part("position", position) if position is not None else None
         self.q_width, self.kv_width = self.nh * self.hd, self.nkv * self.hd
+        self.hdv = int(v_head_dim) if v_head_dim is not None else self.hd
+        self.block = int(block) if block else None
+        self.head_gate, self.own_kv = bool(head_gate), bool(own_kv)
+        if self.block is not None and self.block < 1:
+            raise ValueError("attention: a block mask needs a positive block size")
+        self.o_width, self.v_width = self.nh * self.hdv, self.nkv * self.hdv
+        self.general = self.hdv != self.hd or self.block is not None or self.head_gate or not self.own_kv
         self.wqkv = self.wo = self.q_norm = self.k_norm = None
 
     def weight_specs(self):
-        s = [WeightSpec("q_proj.weight", (self.q_width, self.width)),
-             WeightSpec("k_proj.weight", (self.kv_width, self.width)),
-             WeightSpec("v_proj.weight", (self.kv_width, self.width)),
-             WeightSpec("o_proj.weight", (self.width, self.q_width))]
+        s = [WeightSpec("q_proj.weight", (self.q_width, self.width))]
+        if self.own_kv:
+            s += [WeightSpec("k_proj.weight", (self.kv_width, self.width)),
+                  WeightSpec("v_proj.weight", (self.v_width, self.width))]
+        s.append(WeightSpec("o_proj.weight", (self.width, self.o_width)))
         if self.qk_norm:
-            s += [WeightSpec("q_norm.weight", (self.hd,), "vector", ("one_plus_normal", 0.05)),
-                  WeightSpec("k_norm.weight", (self.hd,), "vector", ("one_plus_normal", 0.05))]
+            s.append(WeightSpec("q_norm.weight", (self.hd,), "vector", ("one_plus_normal", 0.05)))
+            if self.own_kv:
+                s.append(WeightSpec("k_norm.weight", (self.hd,), "vector", ("one_plus_normal", 0.05)))
+        if self.head_gate:
+            s.append(WeightSpec("gate_proj.weight", (self.nh, self.width)))
         return s
 
     def cache_need(self):
-        return KVNeed(self.nkv, self.hd, self.window)
+        return KVNeed(self.nkv, self.hd, self.window, self.hdv if self.hdv != self.hd else None)
 
     def kernel_needs(self, run_dtype):
         from ..kernels import attn_tc, catalog
         if run_dtype != torch.bfloat16:
             return [("attn_simple.cu", ())]
+        if self.general:
+            out = [("attn_simple.cu", ())]
+            if self._fast_attention() and attn_tc.BLOCK_MASK:
+                out.append(attn_tc.target(self.hd))
+                if self.hd in catalog.TC_HEAD_DIMS:
+                    out.append(attn_tc.tc_target(self.hd))
+            return out
         if self.hd % 16 == 0 and 16 <= self.hd <= 256:
             out = [attn_tc.target(self.hd)]
             if self.hd in catalog.TC_HEAD_DIMS:
@@ -66,22 +97,71 @@ class Attention(Mixer):
             return out
         return [("attn_simple.cu", ())]
 
+    def _fast_attention(self) -> bool:
+        """Whether a general layer's attention itself can still go to the tensor-core kernels: equal head
+        sizes of a kind they take; the block mask they know, the gate is applied behind them."""
+        return self.hdv == self.hd and self.hd % 16 == 0 and 16 <= self.hd <= 256
+
     def bind(self, tensors, rt):
-        if self.hd % 2 or self.hd > ops.MAX_HEAD_DIM:
+        if (self.hd % 2 and not self.general) or self.hd > ops.MAX_HEAD_DIM or self.hdv > ops.MAX_HEAD_DIM:
             raise ValueError(f"attention: head size {self.hd} is not one the kernels take (even, at most "
                              f"{ops.MAX_HEAD_DIM})")
-        ws = [tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        ws = [tensors["q_proj.weight"]]
+        if self.own_kv:
+            ws += [tensors["k_proj.weight"], tensors["v_proj.weight"]]
+        if self.head_gate:
+            ws.append(tensors["gate_proj.weight"])
         if len({w.dtype for w in ws}) != 1:
             raise ValueError("q, k and v projections must share one element type")
         self.wqkv = torch.cat(ws, dim=0).contiguous()
         self.wo = tensors["o_proj.weight"].contiguous()
         if self.qk_norm:
             self.q_norm = tensors["q_norm.weight"].float().contiguous()
-            self.k_norm = tensors["k_norm.weight"].float().contiguous()
+            if self.own_kv:
+                self.k_norm = tensors["k_norm.weight"].float().contiguous()
         if self.position is not None:
             self.position.bind({}, rt)
+            if self.general and self.position.rotation() is None:
+                raise ValueError("attention: with a block mask, a gate, unequal head sizes or shared keys the "
+                                 "position encoding must be a rotation of pairs")
+            if self.general and self.position.rotation().interleaved:
+                raise ValueError("attention: the general kernels rotate pairs (j, j + rotary_dim / 2) only")
+
+    def _forward_general(self, h, residual, batch, cache, rt):
+        """One product [q | k | v | gate] in float32, placement (norm, rotation, cache write), attention
+        with the block mask, the gate, the output projection."""
+        T = h.shape[0]
+        kv = cache.kv
+        if kv.owner != self.own_kv:
+            raise ValueError("attention: a layer without keys and values of its own must read another run's "
+                             "cache, and one with them must own its cache")
+        rot = self.position.rotation() if self.position is not None else None
+        x = rt.arena.alloc((T, self.wqkv.shape[0]), torch.float32)
+        rt.matmul(h, self.wqkv, x)
+        q = rt.arena.alloc((T, self.q_width), rt.dtype)
+        k_off = self.q_width if self.own_kv else None
+        v_off = self.q_width + self.kv_width if self.own_kv else None
+        g_off = self.q_width + (self.kv_width + self.v_width if self.own_kv else 0)
+        rt.launches += 1
+        ops.qkv_place(x, 0, k_off, v_off, q, self.q_norm, self.k_norm, rot.cos if rot else None,
+                      rot.sin if rot else None, rot.dim if rot else 0, batch.tok_pos, batch.tok_seq, kv.k, kv.v,
+                      kv.table, kv.ring, kv.page, self.nh, self.nkv, self.hd, self.hdv, self.eps)
+        gate = x[:, g_off:g_off + self.nh] if self.head_gate else None
+        o = rt.arena.alloc((T, self.o_width), rt.dtype)
+        if self._fast_attention() and rt.attention_fast(q, kv, o, batch, self.nh, self.nkv, self.hd, self.scale,
+                                                        self.block):
+            if gate is not None:
+                rt.launches += 1
+                ops.head_gate(o, gate, self.nh, self.hdv)
+        else:
+            rt.launches += 1
+            ops.attn_simple(q, kv.k, kv.v, o, batch.tok_pos, batch.tok_seq, kv.table, kv.ring, kv.page, self.nh,
+                            self.nkv, self.hd, kv.window, self.scale, v_head_dim=self.hdv, block=self.block, gate=gate)
+        rt.matmul(o, self.wo, residual, ops.EPI_ADD)
 
     def forward(self, h, residual, batch, cache, rt):
+        if self.general:
+            return self._forward_general(h, residual, batch, cache, rt)
         T = h.shape[0]
         kv = cache.kv
         # A position encoding that describes itself as a rotation of pairs is applied by the kernels

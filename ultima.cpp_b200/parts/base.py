@@ -70,10 +70,12 @@ def build_part(family: str, spec: PartSpec):
 # ---------------------------------------------------------------------------------------
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values for every position (``window`` None) or for the last ``window``."""
+    """Keys and values for every position (``window`` None) or for the last ``window``.
+    ``v_head_dim``: the values' head size where it is not the keys'."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -149,7 +151,8 @@ class Position(Part):
 
 class Mixer(Part):
     def cache_need(self):
-        """None, a KVNeed, a StateNeed, or a tuple of both."""
+        """None, a KVNeed, a StateNeed, or a tuple of them (at most one KVNeed; several StateNeeds
+        come back in the run's ``states`` in the order they are named here)."""
         return None
 
     def forward(self, h, residual, batch, cache, rt) -> None:
@@ -238,6 +241,17 @@ class ModelSpec:
     head: PartSpec
     head_name: str
     stop_token_ids: tuple = ()
+    # ((name a part asks for, name the file stores), ...): for checkpoints whose tensor names do not
+    # follow "prefix + the part's own name" (names without ".weight", say)
+    renames: tuple = ()
+
+    def stored_name(self, name: str) -> str:
+        """The name under which the file holds the tensor a part calls ``name`` (prefix included)."""
+        table = self.__dict__.get("_renames")
+        if table is None:
+            table = dict(self.renames)
+            object.__setattr__(self, "_renames", table)
+        return table.get(name, name)
 
     def parts_with_names(self):
         """(name prefix, family, PartSpec) for every part that owns weights."""
@@ -253,7 +267,7 @@ class ModelSpec:
         specs, seen = [], set()
         for prefix, family, ps in self.parts_with_names():
             for s in build_part(family, ps).weight_specs():
-                name = prefix + s.name
+                name = self.stored_name(prefix + s.name)
                 if name in seen:
                     continue
                 seen.add(name)

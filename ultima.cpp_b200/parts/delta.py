@@ -1,0 +1,111 @@
+"""The gated delta-rule mixer: a recurrent layer with a matrix of state a head."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.spec import WeightSpec
+from .base import Mixer, StateNeed, register_part
+
+
+@register_part("mixer", "gated_delta")
+class GatedDelta(Mixer):
+    """For each head a matrix S [key size D, value size E] in float32, zero at a sequence's start.
+    A token brings q, k (``n_kv_heads`` heads of size D; head h uses q/k head h // (heads / kv heads))
+    and v (``n_heads`` heads of size E), each from its projection through a causal convolution of
+    ``conv`` taps over time (one filter a channel, the last tap on the current token, zeros before the
+    sequence) and SiLU; q and k are made unit vectors (x / sqrt(sum x^2 + unit_eps)), q also times
+    D^-1/2.  With the write strength b = sigmoid(b_proj h) (one a head) and the decay
+    a = exp(-exp(a_log[h]) * softplus(decay_up(decay_down h) + dt_bias)) (one a head and key channel):
+
+        S[d, :] *= a[d];   u = b (v - S^T k);   S += k u^T;   o = S^T q
+
+    o is divided by its root mean square over E (``eps``), multiplied by a weight of size E shared by
+    the heads and by sigmoid(gate_up(gate_down h)), and goes through the output projection into the
+    stream the mixer is handed.  The convolution's last ``conv - 1`` inputs are state too.
+
+    Everything between the projections and the output projection is float32.  The projections that
+    read the mixer's input run as one product [q | k | v | b | decay_down | gate_down]; the two
+    low-rank up-projections are folded into the kernels that use their results.
+    """
+
+    graph_safe = True
+
+    def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, v_head_dim: int, conv: int,
+                 decay_rank: int, gate_rank: int, eps: float, unit_eps: float = 1e-6):
+        if n_heads % n_kv_heads:
+            raise ValueError("heads must be a multiple of kv heads")
+        self.width, self.nh, self.nkv = int(width), int(n_heads), int(n_kv_heads)
+        self.hd, self.hdv, self.conv = int(head_dim), int(v_head_dim), int(conv)
+        self.decay_rank, self.gate_rank = int(decay_rank), int(gate_rank)
+        self.eps, self.unit_eps = float(eps), float(unit_eps)
+        self.qk_width, self.v_width = self.nkv * self.hd, self.nh * self.hdv
+        self.channels = 2 * self.qk_width + self.v_width
+        if not (1 <= self.conv <= 16):
+            raise ValueError(f"gated_delta: a convolution of {self.conv} taps is not one the kernels take (1 to 16)")
+        if self.hd > 256:
+            raise ValueError(f"gated_delta: key size {self.hd} is more than the scan kernel holds (256)")
+        if not (1 <= self.decay_rank <= 256 and 1 <= self.gate_rank <= 256):
+            raise ValueError("gated_delta: the low-rank products take inner sizes of 1 to 256")
+
+    def weight_specs(self):
+        W, V = WeightSpec, "vector"
+        return [W("q_proj.weight", (self.qk_width, self.width)), W("q_conv.weight", (self.qk_width, self.conv), V, ("normal", 0.3)),
+                W("k_proj.weight", (self.qk_width, self.width)), W("k_conv.weight", (self.qk_width, self.conv), V, ("normal", 0.3)),
+                W("v_proj.weight", (self.v_width, self.width)), W("v_conv.weight", (self.v_width, self.conv), V, ("normal", 0.3)),
+                W("b_proj.weight", (self.nh, self.width)),
+                W("a_log", (self.nh,), V, ("normal", 0.5)),
+                W("o_norm.weight", (self.hdv,), V, ("one_plus_normal", 0.05)),
+                W("decay_down.weight", (self.decay_rank, self.width)),
+                W("decay_up.weight", (self.nh * self.hd, self.decay_rank), V, ("normal", 0.1)),
+                W("dt_bias", (self.nh * self.hd,), V, ("normal", 0.5)),
+                W("gate_down.weight", (self.gate_rank, self.width)),
+                W("gate_up.weight", (self.v_width, self.gate_rank), V, ("normal", 0.1)),
+                W("o_proj.weight", (self.width, self.v_width))]
+
+    def cache_need(self):
+        taps = max(self.conv - 1, 1)
+        return (StateNeed((self.nh, self.hd, self.hdv), "float32"), StateNeed((taps, self.channels), "float32"))
+
+    def kernel_needs(self, run_dtype):
+        return [("delta.cu", ())]
+
+    def bind(self, tensors, rt):
+        ws = [tensors[n + ".weight"] for n in ("q_proj", "k_proj", "v_proj", "b_proj", "decay_down", "gate_down")]
+        if len({w.dtype for w in ws}) != 1:
+            raise ValueError("gated_delta: the projections of the mixer's input must share one element type")
+        self.w_in = torch.cat(ws, dim=0).contiguous()
+        self.b_off = self.channels
+        self.a_off = self.b_off + self.nh
+        self.g_off = self.a_off + self.decay_rank
+        self.conv_w = torch.cat([tensors[n].float() for n in ("q_conv.weight", "k_conv.weight", "v_conv.weight")],
+                                dim=0).contiguous()
+        self.decay_up = tensors["decay_up.weight"].float().contiguous()
+        self.gate_up = tensors["gate_up.weight"].float().contiguous()
+        self.dt_bias = tensors["dt_bias"].float().contiguous()
+        self.a_log = tensors["a_log"].float().contiguous()
+        self.o_norm = tensors["o_norm.weight"].float().contiguous()
+        self.wo = tensors["o_proj.weight"].contiguous()
+        self.shape = ops.delta_shape(self.nh, self.nkv, self.hd, self.hdv, self.conv, self.decay_rank, self.gate_rank,
+                                     (0, self.qk_width, 2 * self.qk_width, self.b_off, self.a_off, self.g_off))
+
+    def forward(self, h, residual, batch, cache, rt):
+        T = h.shape[0]
+        S, conv_state = cache.states
+        f32 = torch.float32
+        p = rt.arena.alloc((T, self.w_in.shape[0]), f32)
+        rt.matmul(h, self.w_in, p)
+        qn = rt.arena.alloc((T, self.qk_width), f32)
+        kn = rt.arena.alloc((T, self.qk_width), f32)
+        vc = rt.arena.alloc((T, self.v_width), f32)
+        beta = rt.arena.alloc((T, self.nh), f32)
+        dec = rt.arena.alloc((T, self.nh * self.hd), f32)
+        o = rt.arena.alloc((T, self.v_width), f32)
+        oa = rt.arena.alloc((T, self.v_width), rt.dtype)
+        rt.launches += 4
+        ops.delta_prepare(p, self.shape, self.conv_w, conv_state, self.decay_up, self.dt_bias, self.a_log, batch,
+                          qn, kn, vc, beta, dec, self.unit_eps, self.hd ** -0.5)
+        ops.conv_state_update(p, conv_state, batch, self.channels, self.conv)
+        ops.delta_scan(qn, kn, vc, beta, dec, o, S, batch, self.nh, self.nkv, self.hd, self.hdv)
+        ops.delta_finish(o, p, self.g_off, self.gate_rank, self.gate_up, self.o_norm, oa, self.nh, self.hdv, self.eps)
+        rt.matmul(oa, self.wo, residual, ops.EPI_ADD)

@@ -51,3 +51,38 @@ class GatedSiLU(FeedForward):
         else:
             rt.matmul(h, self.wgu[:self.inner], a, ops.EPI_SWIGLU, w2=self.wgu[self.inner:])
         rt.matmul(a, self.wd, residual, ops.EPI_ADD)
+
+
+@register_part("feed_forward", "gated_clamped")
+class GatedClamped(FeedForward):
+    """down(g' * sigmoid(alpha g') * (u' + shift)) with g' = min(gate(h), limit) and
+    u' = clamp(up(h), -limit, limit); no biases; added to the stream it is handed.  Gate and up are one
+    matrix [gate ; up] and one product; the gate product is formed in float32 from the float32 sums."""
+
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, limit: float, alpha: float = 1.702, shift: float = 1.0):
+        self.width, self.inner = int(width), int(inner)
+        self.limit, self.alpha, self.shift = float(limit), float(alpha), float(shift)
+        self.wgu = self.wd = None
+
+    def weight_specs(self):
+        return [WeightSpec("gate_proj.weight", (self.inner, self.width)),
+                WeightSpec("up_proj.weight", (self.inner, self.width)),
+                WeightSpec("down_proj.weight", (self.width, self.inner))]
+
+    def bind(self, tensors, rt):
+        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        if g.dtype != u.dtype:
+            raise ValueError("gate and up projections must share one element type")
+        self.wgu = torch.cat([g, u], dim=0).contiguous()
+        self.wd = tensors["down_proj.weight"].contiguous()
+
+    def forward(self, h, residual, batch, rt):
+        T = h.shape[0]
+        gu = rt.arena.alloc((T, 2 * self.inner), torch.float32)
+        rt.matmul(h, self.wgu, gu)
+        a = rt.arena.alloc((T, self.inner), rt.dtype)
+        rt.launches += 1
+        ops.glu_clamped(gu, a, self.limit, self.alpha, self.shift)
+        rt.matmul(a, self.wd, residual, ops.EPI_ADD)

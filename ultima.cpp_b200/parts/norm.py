@@ -28,3 +28,9 @@ class RMSNorm(Norm):
         rt.launches += 1
         ops.rmsnorm(x, self.weight, out, self.eps, rows)
         return out
+
+    def add_normed(self, y, x, rt, h=None, clear=False):
+        """x += norm(y), for layers that norm a sublayer's output instead of its input; x, y float32
+        [T, width].  ``h`` receives the new x in h's type (the next sublayer's input); ``clear`` zeroes y."""
+        rt.launches += 1
+        ops.rmsnorm_add(y, self.weight, x, self.eps, h=h, clear_y=clear)

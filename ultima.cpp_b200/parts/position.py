@@ -1,6 +1,8 @@
 """Position encodings.  A mixer that encodes its queries and keys by position holds one of these."""
 from __future__ import annotations
 
+import math
+
 import torch
 
 from ..kernels import ops
@@ -18,20 +20,31 @@ class _Rotary(Position):
     interleaved = False
     graph_safe = True        # tables made at bind; forward launches kernels only
 
-    def __init__(self, head_dim: int, theta: float, max_positions: int, rotary_dim: int | None = None):
+    def __init__(self, head_dim: int, theta: float, max_positions: int, rotary_dim: int | None = None,
+                 wavelength_scaling: tuple | None = None):
+        """``wavelength_scaling`` = (factor, low, high, original): frequencies are rescaled by wavelength
+        l = 2 pi / f.  Short waves (l < original / high) keep f, long ones (l > original / low) get
+        f / factor, and between them f is blended linearly in original / l."""
         self.head_dim, self.theta, self.max_positions = int(head_dim), float(theta), int(max_positions)
+        self.scaling = tuple(float(v) for v in wavelength_scaling) if wavelength_scaling else None
         self.rotary_dim = int(rotary_dim) if rotary_dim is not None else self.head_dim
         if self.rotary_dim % 2 or not (2 <= self.rotary_dim <= self.head_dim):
             raise ValueError(f"rotary size {self.rotary_dim} must be even and at most the head size {self.head_dim}")
         self.cos = self.sin = None
 
     def bind(self, tensors, rt):
-        key = ("rotary", self.rotary_dim, self.theta, self.max_positions)
+        key = ("rotary", self.rotary_dim, self.theta, self.max_positions, self.scaling)
 
         def make():
             half = self.rotary_dim // 2
             j = torch.arange(half, dtype=torch.float64)
             inv = 1.0 / torch.pow(torch.tensor(self.theta, dtype=torch.float64), 2.0 * j / self.rotary_dim)
+            if self.scaling is not None:
+                factor, low, high, original = self.scaling
+                wave = 2.0 * math.pi / inv
+                blend = (original / wave - low) / (high - low)
+                mid = (1.0 - blend) * inv / factor + blend * inv
+                inv = torch.where(wave < original / high, inv, torch.where(wave > original / low, inv / factor, mid))
             ang = torch.arange(self.max_positions, dtype=torch.float64)[:, None] * inv[None, :]
             return (torch.cos(ang).float().contiguous().to(rt.device),
                     torch.sin(ang).float().contiguous().to(rt.device))
