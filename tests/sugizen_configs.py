@@ -49,6 +49,7 @@ WIDE = {"architecture": "Sugizen", "vocab": 384, "width": 128, "norm": {"eps": 1
     _layer("attention", _attention(4, 1, 64, 64, 0.125, _ROT_C, 64), 256, 1.5),
     _layer("attention", _attention(8, 1, 64, 64, 0.125, _ROT_C, 64, kv_from=1), 256, 1.5),
     _layer("attention", _attention(2, 2, 128, 128, 0.09, {"base": 1000.0, "dims": 128}, 100), 128, 3.0),
+    _layer("attention", _attention(6, 3, 48, 48, 0.15, {"base": 1000.0, "dims": 24}, 40), 128, 3.0),
 ]}
 
 CONFIGS = {"mixed": MIXED, "odd": ODD, "wide": WIDE}

@@ -68,6 +68,34 @@ def test_clamped_gate_product_and_head_gate(dtype):
     assert rel_err(o, ref) < (1e-6 if dtype == torch.float32 else 2 ** -7)
 
 
+@pytest.mark.parametrize("T", [5, 300, 1500])
+def test_clamped_gate_product_as_the_tensor_core_products_epilogue(T):
+    """Sums large enough that both clamps are active; few tokens, many, and enough for the two-CTA kernel."""
+    from ultima_b200.engine.runtime import Runtime
+    ops = _ops()
+    rt = Runtime(DEV, torch.bfloat16)
+    g = torch.Generator().manual_seed(T)
+    F, K = 192, 128
+    a = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    wg = (torch.randn(F, K, generator=g) * 0.2).to(torch.bfloat16).to(DEV)
+    wu = (torch.randn(F, K, generator=g) * 0.2).to(torch.bfloat16).to(DEV)
+    wgu = torch.stack([wg.view(F // 64, 64, K), wu.view(F // 64, 64, K)], dim=1).reshape(2 * F, K).contiguous()
+    for limit, alpha, shift in ((1.5, 1.702, 1.0), (0.5, 1.0, 0.0)):
+        gate = torch.clamp(a.double() @ wg.double().T, max=limit)
+        up = torch.clamp(a.double() @ wu.double().T, -limit, limit)
+        assert float((gate == limit).double().mean()) > 0.1 and float((up.abs() == limit).double().mean()) > 0.2
+        ref = gate * torch.sigmoid(alpha * gate) * (up + shift)
+        out = torch.empty(T, F, dtype=torch.bfloat16, device=DEV)
+        rt.matmul(a, wgu, out, ops.EPI_SWIGLU_IL, gate=(limit, alpha, shift))
+        rt.check_status()
+        assert rel_err(out, ref) < 2 ** -6, (T, limit)
+    # without the constants the epilogue is the plain silu(g) * u
+    out = torch.empty(T, F, dtype=torch.bfloat16, device=DEV)
+    rt.matmul(a, wgu, out, ops.EPI_SWIGLU_IL)
+    gsum, usum = a.double() @ wg.double().T, a.double() @ wu.double().T
+    assert rel_err(out, gsum * torch.sigmoid(gsum) * usum) < 2 ** -6
+
+
 def _paged(k, v, ring_pages, seed):
     """k [n, nkv, hd], v [n, nkv, hdv] into shuffled pages of 64 positions."""
     n, nkv, hd = k.shape
@@ -130,6 +158,61 @@ def test_a_key_just_outside_a_block_is_not_seen_and_one_just_inside_is():
             inside = first <= marked <= p <= last
             got = float(out[i, :hd].mean())
             assert (got > 4.9) if inside else (abs(got) < 1.0), (block, marked, p, got)
+
+
+class _View:
+    def __init__(self, k, v, table, ring):
+        self.k, self.v, self.table, self.ring, self.page, self.window, self.owner = k, v, table, ring, 64, None, True
+
+
+class _Step:
+    def __init__(self, befores, news):
+        start = [0]
+        for n in news:
+            start.append(start[-1] + n)
+        self.seq_start = torch.tensor(start, dtype=torch.int32, device=DEV)
+        self.seq_before = torch.tensor(befores, dtype=torch.int32, device=DEV)
+        self.n_seqs, self.max_new, self.max_after = len(news), max(news), max(b + n for b, n in zip(befores, news))
+
+
+@pytest.mark.parametrize("hd,kernel", [(64, None), (128, None), (96, None), (48, None), (64, "mma"), (128, "tc")])
+def test_the_tensor_core_attention_kernels_keep_to_the_block(hd, kernel):
+    """The same marked key for the kernels that prompts and single tokens of the bfloat16 path use (tcgen05 and
+    mma.sync for prompts; TMA-fed, cp.async and tcgen05 for single tokens): every row of a prompt, and single
+    tokens at the places around the block's edges, must see the marked key exactly when it lies in their block
+    and not after them."""
+    from ultima_b200.engine.runtime import Runtime
+    from ultima_b200.kernels import attn_tc
+    rt = Runtime(DEV, torch.bfloat16)
+    nh, nkv, n = 4, 2, 640
+    for block, marked in ((64, 128), (64, 191), (100, 300), (100, 399), (250, 250), (37, 36)):
+        g = torch.Generator().manual_seed(block + marked + hd)
+        k = (torch.randn(n, nkv, hd, generator=g) * 0.1)
+        v = (torch.randn(n, nkv, hd, generator=g) * 0.1)
+        qdir = torch.randn(hd, generator=g)
+        k[marked] = qdir * 40.0
+        v[marked] = 5.0
+        kc, vc, table = _paged(k.to(torch.bfloat16), v.to(torch.bfloat16), 10, seed=block)
+        kv = _View(kc, vc, table, 640)
+        first, last = marked - marked % block, min(n, marked - marked % block + block) - 1
+        q_all = (qdir * 0.5).repeat(n, nh).to(torch.bfloat16).to(DEV)
+        if kernel != "tc":                                      # a prompt of all 640 positions
+            out = torch.full((n, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+            attn_tc.attention(q_all, kv, out, _Step([0], [n]), nh, nkv, hd, 1.0, rt, kernel=kernel, block=block)
+            rt.check_status()
+            got = out.float().view(n, nh, hd).mean(-1).cpu()
+            for p in range(n):
+                inside = first <= marked <= p <= last
+                assert bool((got[p] > 4.8).all()) if inside else bool((got[p].abs() < 1.0).all()), (hd, block, marked, p, got[p])
+        for p in {marked, marked + 1, last, last + 1, first - 1, n - 1}:          # single tokens
+            if not 0 <= p < n:
+                continue
+            out = torch.full((1, nh * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+            attn_tc.attention(q_all[:1], kv, out, _Step([p], [1]), nh, nkv, hd, 1.0, rt, kernel=kernel, block=block)
+            rt.check_status()
+            got = out.float().view(nh, hd).mean(-1).cpu()
+            inside = first <= marked <= p <= last
+            assert bool((got > 4.8).all()) if inside else bool((got.abs() < 1.0).all()), (hd, block, marked, p, got)
 
 
 def _scan_inputs(T, H, G, D, E, seed, slow_decay=False):

@@ -122,13 +122,14 @@ template <int NT>
 __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float* m, float* l, float c,
                                              const int* row_pos, bool const* row_ok, int key_pos0, int window, int lane) {
     float mx[2] = {-INFINITY, -INFINITY};
+    const int row_lo[2] = {span_lo(row_pos[0], window), span_lo(row_pos[1], window)};
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
             const int kp = key_pos0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-            const bool ok = row_ok[r] && kp <= row_pos[r] && (window <= 0 || kp > row_pos[r] - window);
+            const bool ok = row_ok[r] && kp <= row_pos[r] && kp >= row_lo[r];
             const float v = ok ? s[nt][e] * c : -INFINITY;
             s[nt][e] = v;
             mx[r] = fmaxf(mx[r], v);

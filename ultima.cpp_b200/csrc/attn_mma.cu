@@ -68,8 +68,7 @@ attn_prefill_kernel(AttnParams p, PagedKV c) {
     }
     const int tok_first = R0 / G, tok_last = min(q_len - 1, (R0 + 63) / G);
     const int pos_hi = before + tok_last;
-    int pos_lo = 0;
-    if (p.window > 0) pos_lo = max(0, before + tok_first - p.window + 1);
+    const int pos_lo = span_lo(before + tok_first, p.window);
     const int t_lo = pos_lo / KT, t_hi = pos_hi / KT;
 
     float o[DTILES][4];
@@ -125,8 +124,7 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
     const int G = p.group;
     const int row = p.seq_start[seq];              // the sequence's one token
     const int pos = p.seq_before[seq];             // its position; keys [lo, pos]
-    int lo = 0;
-    if (p.window > 0) lo = max(0, pos - p.window + 1);
+    const int lo = span_lo(pos, p.window);
     const int t_first = lo / KT, t_last = pos / KT;
     const int n_tiles = t_last - t_first + 1;
     const int per = (n_tiles + p.n_slices - 1) / p.n_slices;
@@ -314,8 +312,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int G = p.group;
     const int row = p.seq_start[seq];
     const int pos = p.seq_before[seq];
-    int lo = 0;
-    if (p.window > 0) lo = max(0, pos - p.window + 1);
+    const int lo = span_lo(pos, p.window);
     const int t_first = lo / KT, t_last = pos / KT;
     const int all_tiles = t_last - t_first + 1;
     const int per = (all_tiles + p.n_slices - 1) / p.n_slices;

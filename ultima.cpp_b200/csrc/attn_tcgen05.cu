@@ -142,8 +142,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int last_pos = before + q_len - 1;
     const int tok_last = min(q_len - 1, tok_first + TPB - 1);
     const int pos_hi = before + tok_last;
-    int pos_lo = 0;
-    if (p.window > 0) pos_lo = max(0, before + tok_first - p.window + 1);
+    const int pos_lo = span_lo(before + tok_first, p.window);
     int t_lo = pos_lo / BN, n_tiles = pos_hi / BN - t_lo + 1;
     if (DECODE) {                                          // this CTA's slice of the tiles (may be empty)
         const int per = (n_tiles + p.n_slices - 1) / p.n_slices;
@@ -312,12 +311,13 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             tmem_ld_wait();
             // scores stay raw (q.k); the scale goes into the exponent: p = 2^(s c - m).  A tile that
             // every row of the CTA sees whole needs no mask.
-            const bool whole = row_ok && base + BN - 1 <= before + tok_first && p.window <= 0 && r < TPB * G;
+            const bool whole = row_ok && base + BN - 1 <= before + tok_first && p.window == 0 && r < TPB * G;
             if (!__all_sync(0xffffffffu, whole)) {
+                const int row_lo = span_lo(row_pos, p.window);
 #pragma unroll
                 for (int cI = 0; cI < BN; ++cI) {
                     const int kp = base + cI;
-                    const bool vis = row_ok && kp <= row_pos && (p.window <= 0 || kp > row_pos - p.window);
+                    const bool vis = row_ok && kp <= row_pos && kp >= row_lo;
                     if (!vis) raw[cI] = __float_as_uint(-INFINITY);
                 }
             }
@@ -483,7 +483,7 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         has[t] = tokf[t] < q_len;
         const int tokl = min(q_len - 1, tokf[t] + TPB - 1);
         hi[t] = (before + tokl) / BN;
-        lo[t] = p.window > 0 ? max(0, before + tokf[t] - p.window + 1) / BN : 0;
+        lo[t] = span_lo(before + tokf[t], p.window) / BN;
     }
     const int t_lo = lo[0];
     const int t_hi = has[1] ? hi[1] : hi[0];
@@ -674,12 +674,13 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
             tmem_ld32(s_base + (uint32_t)(b * BN), raw);
             tmem_ld32(s_base + (uint32_t)(b * BN + 32), raw + 32);
             tmem_ld_wait();
-            const bool whole = row_ok && base + BN - 1 <= before + tokf[t] && p.window <= 0;
+            const bool whole = row_ok && base + BN - 1 <= before + tokf[t] && p.window == 0;
             if (!__all_sync(0xffffffffu, whole)) {
+                const int row_lo = span_lo(row_pos, p.window);
 #pragma unroll
                 for (int cI = 0; cI < BN; ++cI) {
                     const int kp = base + cI;
-                    const bool vis = row_ok && kp <= row_pos && (p.window <= 0 || kp > row_pos - p.window);
+                    const bool vis = row_ok && kp <= row_pos && kp >= row_lo;
                     if (!vis) raw[cI] = __float_as_uint(-INFINITY);
                 }
             }

@@ -134,6 +134,15 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return red[32];
 }
 
+// The lowest position a token at ``pos`` sees under the mask ``w`` that the attention kernels take as one
+// integer: w > 0, the last w positions (a sliding window); w < 0, blocks of -w positions counted from the
+// sequence's start (a token sees the earlier tokens of its own block); 0, everything before it.
+__device__ __forceinline__ int span_lo(int pos, int w) {
+    if (w > 0) return max(0, pos - w + 1);
+    if (w < 0) return pos - pos % (-w);
+    return 0;
+}
+
 // Where a sequence's position lies in a paged cache.  A sequence's pages are listed in
 // ``table`` (``pages_per_seq`` entries for each sequence of the step); ``ring`` is the
 // number of positions the sequence's storage holds (a multiple of the page size): a full

@@ -46,7 +46,22 @@ struct GemmParams {
     int atomic;           // EPI_ADD: add with atomics (K is split)
     int share_tail;       // persistent EPI_ADD: the tiles of the last, part-empty round are shared out by k blocks
     int* error;           // raised on a timeout
+    // the gate product's constants: out = g' / (1 + exp(-alpha g')) * (u' + shift) with g' = min(g, limit) and
+    // u' = clamp(u, -limit, limit); +inf, 1 and 0 give silu(g) * u with the same bits as without them
+    float act_limit, act_alpha, act_shift;
 };
+
+__device__ __forceinline__ float gate_product(const GemmParams& p, float g, float u) {
+    g = fminf(g, p.act_limit);
+    u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
+    return g / (1.0f + __expf(-p.act_alpha * g)) * (u + p.act_shift);
+}
+
+static void set_gate_constants(GemmParams& p, const float* gate) {
+    p.act_limit = gate ? gate[0] : INFINITY;
+    p.act_alpha = gate ? gate[1] : 1.0f;
+    p.act_shift = gate ? gate[2] : 0.0f;
+}
 
 template <int BN, int EPI>
 struct Smem {
@@ -97,7 +112,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                     if (t >= p.T) break;
                     const float own = __uint_as_float(up ? r[8 + c] : r[c]), other = xch[col * 64 + fl];
                     const float g = up ? other : own, u = up ? own : other;
-                    out[(long long)t * p.ldo + f] = from_f32<TO>(g / (1.0f + __expf(-g)) * u);
+                    out[(long long)t * p.ldo + f] = from_f32<TO>(gate_product(p, g, u));
                 }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -115,7 +130,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t tmem
                     asm volatile("red.global.add.f32 [%0], %1;" ::"l"(dst), "f"(v) : "memory");
                 } else {
                     const float u = __uint_as_float(r2[c]);
-                    *dst = from_f32<TO>(v / (1.0f + __expf(-v)) * u);
+                    *dst = from_f32<TO>(gate_product(p, v, u));
                 }
             }
         }
@@ -697,11 +712,12 @@ static int launch_bn(const CUtensorMap* mw, const CUtensorMap* mw2, const CUtens
 }
 
 // map_w (and map_w2 for EPI_SWIGLU): weights [N, K], boxes of 128 rows; map_a: activations [T, K],
-// boxes of ``bn`` rows.  splits > 1 cuts K into slices of kb_per_split blocks of 64: EPI_ADD then adds
+// boxes of ``bn`` rows.  ``gate`` (host, three floats or null): limit, alpha and shift of the gate product.
+// splits > 1 cuts K into slices of kb_per_split blocks of 64: EPI_ADD then adds
 // with atomics, EPI_STORE (float32 only) writes slice z at out + z * split_stride.
 UB_API int ub_gemm_tc(const void* map_w, const void* map_w2, const void* map_a, void* out, int o_dtype, long long ldo,
                       long long split_stride, int T, int N, int K, int bn, int epi, int splits, int* error,
-                      cudaStream_t st) {
+                      const float* gate, cudaStream_t st) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || splits < 1) return UB_ERR_ARG;
     if (splits > 1 && (epi == EPI_SWIGLU || epi == EPI_SWIGLU_IL)) return UB_ERR_ARG;
@@ -715,6 +731,7 @@ UB_API int ub_gemm_tc(const void* map_w, const void* map_w2, const void* map_a, 
     p.atomic = (epi == EPI_ADD && splits > 1) ? 1 : 0;
     p.share_tail = 0;
     p.error = error;
+    set_gate_constants(p, gate);
     if ((long long)(splits - 1) * p.kb_per_split >= nkb) return UB_ERR_ARG;      // an empty slice
     const CUtensorMap* mw = (const CUtensorMap*)map_w;
     const CUtensorMap* mw2 = (const CUtensorMap*)(map_w2 ? map_w2 : map_w);
@@ -759,7 +776,7 @@ static int launch_pair(const CUtensorMap* mw, const CUtensorMap* ma, GemmParams 
 }
 
 UB_API int ub_gemm_tc_pair(const void* map_w, const void* map_a, void* out, int o_dtype, long long ldo, int T, int N,
-                           int K, int epi, int* error, cudaStream_t st) {
+                           int K, int epi, int* error, const float* gate, cudaStream_t st) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0) return UB_ERR_ARG;
     if (epi == EPI_SWIGLU_IL && (N % 128) != 0) return UB_ERR_ARG;
@@ -768,6 +785,7 @@ UB_API int ub_gemm_tc_pair(const void* map_w, const void* map_a, void* out, int 
     p.T = T; p.N = N; p.K = K;
     p.kb_per_split = (K + BK - 1) / BK;
     p.atomic = 0; p.share_tail = 0; p.error = error;
+    set_gate_constants(p, gate);
     const CUtensorMap* mw = (const CUtensorMap*)map_w;
     const CUtensorMap* ma = (const CUtensorMap*)map_a;
     if (epi == EPI_STORE && o_dtype == UB_BF16) return launch_pair<EPI_STORE, __nv_bfloat16>(mw, ma, p, st);

@@ -109,16 +109,19 @@ class Runtime:
             raise RuntimeError("a wait inside a kernel ran out of time; the step's results are not valid")
 
     # ---- products ----------------------------------------------------------------------
-    def matmul(self, a, w, out, epilogue=ops.EPI_STORE, w2=None):
-        """out (=, +=) a @ w.T with float32 accumulation; see kernels.ops for the epilogues."""
+    def matmul(self, a, w, out, epilogue=ops.EPI_STORE, w2=None, gate=None):
+        """out (=, +=) a @ w.T with float32 accumulation; see kernels.ops for the epilogues.  ``gate`` =
+        (limit, alpha, shift): the constants of a clamped gate product (tensor-core epilogues only)."""
         self.launches += 1
         if self.use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
             from ..kernels import gemm_tc
-            key = gemm_tc.launch_key(a, w, out, epilogue, w2, self._status_ptr)
+            key = gemm_tc.launch_key(a, w, out, epilogue, w2, self._status_ptr, gate)
             if gemm_tc.relaunch(key):
                 return None
             if gemm_tc.accepts(a, w, out, epilogue, w2):
-                return gemm_tc.gemm(a, w, out, epilogue, w2, self, key=key)
+                return gemm_tc.gemm(a, w, out, epilogue, w2, self, key=key, gate=gate)
+        if gate is not None:
+            raise ops.KernelError("a clamped gate product is an epilogue of the tensor-core product only")
         if epilogue == ops.EPI_SWIGLU_IL:
             raise ops.KernelError("the interleaved gate/up layout is for the tensor-core product only; "
                                   "this call does not fit it (operand alignment)")

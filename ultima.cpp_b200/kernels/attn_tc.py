@@ -111,7 +111,8 @@ def _tc_map(key, make):
     return addr
 
 
-def run_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, decode: bool, n_slices: int = 1):
+def run_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, decode: bool, n_slices: int = 1,
+                mask: int | None = None):
     L = tc_lib(head_dim)
     group = n_heads // n_kv_heads
     T = q.shape[0]
@@ -127,8 +128,8 @@ def run_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, dec
         part_ml = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, 2), torch.float32)
     rc = L.ub_attn_tc(1 if decode else 0, mq, mk, mv, _ptr(out), out.stride(0), _ptr(batch.seq_start),
                       _ptr(batch.seq_before), _ptr(kv.table), kv.table.shape[1], kv.ring, kv.page, batch.n_seqs,
-                      batch.max_new, n_heads, n_kv_heads, int(kv.window or 0), float(scale), n_slices,
-                      _ptr(part_o), _ptr(part_ml), _ptr(rt.status[1:2]), _stream())
+                      batch.max_new, n_heads, n_kv_heads, int(kv.window or 0) if mask is None else mask, float(scale),
+                      n_slices, _ptr(part_o), _ptr(part_ml), _ptr(rt.status[1:2]), _stream())
     _check(rc, "attn_tc")
 
 
@@ -197,7 +198,7 @@ def decode_from_qkv(qkv, q_norm, k_norm, cos, sin, eps, kv, out, batch, n_heads,
 
 # The kernels take the mask as one integer: w > 0, the last w positions; w < 0, blocks of -w positions
 # counted from the sequence's start (a token sees the earlier tokens of its own block); 0, everything before.
-BLOCK_MASK = False
+BLOCK_MASK = True
 
 
 def _mask_arg(kv, block) -> int:
@@ -213,22 +214,24 @@ def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slice
     """kernel: None picks (tcgen05 for prompts where it fits, mma.sync otherwise); "mma" forces the latter.
     ``block``: mask by blocks of this many positions instead of by the cache's window."""
     L = lib(head_dim)
+    mask = _mask_arg(kv, block)
+    reach = block or kv.window                       # how far back a token looks at most (None: to the start)
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1
     group = n_heads // n_kv_heads
     decode = batch.max_new == 1 and group <= 16
     tc_ok = (kernel != "mma" and tcgen05_fits(head_dim, n_heads, n_kv_heads) and out.stride(0) % 8 == 0
              and out.data_ptr() % 16 == 0 and kv.k.is_contiguous() and kv.v.is_contiguous())
     if tc_ok and not decode:
-        return run_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, False)
+        return run_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, False, mask=mask)
     if tc_ok and decode and (USE_TCGEN05_DECODE or kernel == "tc"):
-        n = slices or decode_slices(batch.n_seqs, n_kv_heads, batch.max_after, kv.window, per_sm=1)
-        return run_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, True, n)
+        n = slices or decode_slices(batch.n_seqs, n_kv_heads, batch.max_after, reach, per_sm=1)
+        return run_tcgen05(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, True, n, mask=mask)
     part_o = part_ml = None
     n_slices = 1
     tma = (decode and head_dim % 64 == 0 and kernel in (None, "tma") and (USE_TMA_DECODE or kernel == "tma")
            and kv.k.is_contiguous() and kv.v.is_contiguous())
     if decode:
-        n_slices = slices or decode_slices(batch.n_seqs, n_kv_heads, batch.max_after, kv.window)
+        n_slices = slices or decode_slices(batch.n_seqs, n_kv_heads, batch.max_after, reach)
         if n_slices > 1:
             part_o = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, head_dim), torch.float32)
             part_ml = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, 2), torch.float32)
@@ -239,11 +242,11 @@ def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slice
                      lambda a: L.ub_attn_map_kv(a, kv.v.data_ptr(), kv.v.shape[0], n_kv_heads))
         rc = L.ub_attn_decode_tma(mk, mv, _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(batch.seq_start),
                                   _ptr(batch.seq_before), _ptr(kv.table), kv.table.shape[1], kv.ring, kv.page,
-                                  batch.n_seqs, n_heads, n_kv_heads, int(kv.window or 0), float(scale), n_slices,
+                                  batch.n_seqs, n_heads, n_kv_heads, mask, float(scale), n_slices,
                                   _ptr(part_o), _ptr(part_ml), _ptr(rt.status[1:2]), _stream())
         return _check(rc, "attn_decode_tma")
     rc = L.ub_attn_mma(1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), _ptr(kv.v),
                        _ptr(batch.seq_start), _ptr(batch.seq_before), _ptr(kv.table), kv.table.shape[1], kv.ring,
-                       kv.page, batch.n_seqs, batch.max_new, n_heads, n_kv_heads, int(kv.window or 0), float(scale),
+                       kv.page, batch.n_seqs, batch.max_new, n_heads, n_kv_heads, mask, float(scale),
                        n_slices, _ptr(part_o), _ptr(part_ml), _stream())
     _check(rc, "attn_mma")

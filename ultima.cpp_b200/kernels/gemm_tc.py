@@ -24,10 +24,10 @@ def lib():
         L.ub_tmap_bf16_2d.argtypes = [c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_int]
         L.ub_tmap_bf16_2d.restype = c_int
         L.ub_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_longlong,
-                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]
         L.ub_gemm_tc.restype = c_int
         L.ub_gemm_tc_pair.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int,
-                                      c_void_p, c_void_p]
+                                      c_void_p, c_void_p, c_void_p]
         L.ub_gemm_tc_pair.restype = c_int
         L.ub_gemm_tc_set_pdl.argtypes = [c_int]
         L.ub_gemm_tc_set_pdl.restype = None
@@ -135,9 +135,11 @@ def pairs(T: int, N: int, splits: int, epilogue: int, n_sms: int | None = None) 
     return -(-N // 256) * -(-T // 256) >= (n_sms or sm_count()) // 2
 
 
-def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None = None, key=None):
+def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None = None, key=None, gate=None):
     """out: [T, N]; for EPI_SWIGLU_IL [T, N / 2]; for EPI_STORE with ``splits`` > 1 a float32
-    [splits, T, N] whose sum over the first axis is the product."""
+    [splits, T, N] whose sum over the first axis is the product.  ``gate`` = (limit, alpha, shift): the gate
+    product of the two SWIGLU epilogues becomes g' sigmoid(alpha g') (u' + shift) with g' = min(g, limit) and
+    u' = clamp(u, -limit, limit); None: silu(g) u."""
     T, K = a.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.stride(-1) == 1
@@ -153,17 +155,18 @@ def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None 
         assert s == 1 or epilogue == EPI_ADD
         ldo = out.stride(0)
     L = lib()
+    consts = (ctypes.c_float * 3)(*[float(v) for v in gate]) if gate is not None else None
     if not tile_given and out.dim() == 2 and pairs(T, N, s, epilogue):
         fn, what = L.ub_gemm_tc_pair, "gemm_tc_pair"
         maps = (_tmap_entry(w, 128), _tmap_entry(a, 128))
         args = (maps[0][1], maps[1][1], _ptr(out), BF16 if out.dtype == torch.bfloat16 else F32,
-                out.stride(0), T, N, K, epilogue, _ptr(rt.status[1:2]))
+                out.stride(0), T, N, K, epilogue, _ptr(rt.status[1:2]), consts)
     else:
         fn, what = L.ub_gemm_tc, "gemm_tc"
         maps = (_tmap_entry(w, 128), _tmap_entry(w2, 128) if w2 is not None else (None, 0), _tmap_entry(a, bn))
         args = (maps[0][1], maps[1][1], maps[2][1], _ptr(out),
                 BF16 if out.dtype == torch.bfloat16 else F32, ldo, split_stride, T, N, K, bn, epilogue, s,
-                _ptr(rt.status[1:2]))
+                _ptr(rt.status[1:2]), consts)
     if key is not None:
         if len(_plans) > 8192:
             _plans.clear()
@@ -177,13 +180,13 @@ def gemm(a, w, out, epilogue, w2, rt, splits: int | None = None, bn: int | None 
 _plans: dict = {}
 
 
-def launch_key(a, w, out, epilogue, w2, status_ptr: int):
+def launch_key(a, w, out, epilogue, w2, status_ptr: int, gate=None):
     """Everything a plan depends on: places, shapes and strides of the operands and of the result, the
     epilogue, and the status word the kernel reports to (another engine's tensors may come to lie at the
     same addresses with other shapes)."""
     return (a.data_ptr(), a.shape[0], a.shape[1], a.stride(0), w.data_ptr(), w.shape[0], w.stride(0), out.data_ptr(),
             out.dim(), out.shape[-1], out.stride(-2) if out.dim() > 1 else 0, out.dtype, epilogue,
-            0 if w2 is None else w2.data_ptr(), status_ptr, USE_PAIRS)
+            0 if w2 is None else w2.data_ptr(), status_ptr, USE_PAIRS, gate)
 
 
 def relaunch(key) -> bool:

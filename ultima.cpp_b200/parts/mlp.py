@@ -57,7 +57,9 @@ class GatedSiLU(FeedForward):
 class GatedClamped(FeedForward):
     """down(g' * sigmoid(alpha g') * (u' + shift)) with g' = min(gate(h), limit) and
     u' = clamp(up(h), -limit, limit); no biases; added to the stream it is handed.  Gate and up are one
-    matrix [gate ; up] and one product; the gate product is formed in float32 from the float32 sums."""
+    matrix and one product; the gate product is formed in float32 from the float32 sums.  On the
+    tensor-core path it is the product's epilogue (blocks of 64 gate rows and 64 up rows alternate, as in
+    ``gated_silu``); elsewhere [gate ; up] goes out in float32 and a kernel of its own forms it."""
 
     graph_safe = True
 
@@ -75,11 +77,23 @@ class GatedClamped(FeedForward):
         g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
         if g.dtype != u.dtype:
             raise ValueError("gate and up projections must share one element type")
-        self.wgu = torch.cat([g, u], dim=0).contiguous()
         self.wd = tensors["down_proj.weight"].contiguous()
+        self.interleaved = (rt.use_tensor_cores and g.dtype == torch.bfloat16 and self.inner % 64 == 0
+                            and self.width % 8 == 0)
+        if self.interleaved:
+            n = self.inner // 64
+            self.wgu = torch.stack([g.view(n, 64, self.width), u.view(n, 64, self.width)], dim=1) \
+                .reshape(2 * self.inner, self.width).contiguous()
+        else:
+            self.wgu = torch.cat([g, u], dim=0).contiguous()
 
     def forward(self, h, residual, batch, rt):
         T = h.shape[0]
+        if self.interleaved:
+            a = rt.arena.alloc((T, self.inner), rt.dtype)
+            rt.matmul(h, self.wgu, a, ops.EPI_SWIGLU_IL, gate=(self.limit, self.alpha, self.shift))
+            rt.matmul(a, self.wd, residual, ops.EPI_ADD)
+            return
         gu = rt.arena.alloc((T, 2 * self.inner), torch.float32)
         rt.matmul(h, self.wgu, gu)
         a = rt.arena.alloc((T, self.inner), rt.dtype)
