@@ -414,6 +414,134 @@ def sampling_times(batches=(1, 8, 64), vocab=151936, history=256):
     return 0
 
 
+# ---------------------------------------------------------------------------------------------
+# --only sugizen: the Sugizen design beside Qwen3 at equal layer sizes (random weights)
+# ---------------------------------------------------------------------------------------------
+SUGIZEN_SIZES = {
+    "w2048": dict(width=2048, ff=6144, heads=16, kv_heads=4, dim=128, layers=8, vocab=32768),
+    "w4096": dict(width=4096, ff=12288, heads=32, kv_heads=8, dim=128, layers=8, vocab=32768),
+}
+
+
+def sugizen_config(z):
+    """Layers in fours: delta rule, attention, attention on the first one's keys and values, delta rule."""
+    rot = {"base": 500000.0, "dims": z["dim"] // 2, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+           "rot": rot, "mask": {"size": 1024}}
+    delta = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "conv": 4,
+             "decay_rank": 64, "gate_rank": 64}
+    mlp = {"kind": "dense", "ff": z["ff"], "limit": 7.0}
+    layers = []
+    for i in range(z["layers"]):
+        kind = i % 4
+        if kind in (0, 3):
+            layers.append({"type": "channel_delta", "mixer": dict(delta), "mlp": dict(mlp)})
+        else:
+            m = dict(att)
+            if kind == 2:
+                m["kv_from"] = i - 1
+            layers.append({"type": "attention", "mixer": m, "mlp": dict(mlp)})
+    return {"architecture": "Sugizen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def qwen3_config_like(z):
+    d = dict(QWEN3_8B)
+    d.update(vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=z["layers"],
+             num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["dim"])
+    return d
+
+
+def _kernel_times(run_once):
+    """kernel name -> (launches, total microseconds) of one call of ``run_once`` (CUPTI through torch.profiler)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run_once()
+        torch.cuda.synchronize()
+    out = {}
+    for e in prof.events():
+        if e.device_type != torch.autograd.DeviceType.CUDA:
+            continue
+        name = e.name.split("(")[0].replace("void ", "").split("<")[0][:40]
+        n, t = out.get(name, (0, 0.0))
+        out[name] = (n + 1, t + (e.time_range.end - e.time_range.start))
+    return {k: [v[0], round(v[1], 1)] for k, v in sorted(out.items(), key=lambda kv: -kv[1][1])}
+
+
+def sugizen_times(args):
+    import numpy as np
+    import torch
+    import ultima_b200 as u
+    from ultima_b200.engine import Engine
+    from ultima_b200.weights import random_tensors_on_device
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    rng = np.random.default_rng(0)
+    P, B, K, W = args.prefill_tokens, args.batch, args.steps, max(3, args.warmup)
+    result = {}
+    clocks = ClockSampler()
+    clocks.start()
+    for size, z in SUGIZEN_SIZES.items():
+        result[size] = {}
+        for model, cfg_dict in (("sugizen", sugizen_config(z)), ("qwen3", qwen3_config_like(z))):
+            cfg = u.config_from_dict(cfg_dict)
+            spec = u.model_spec_for(cfg)
+            tensors = random_tensors_on_device(spec.weight_specs(), 0, torch.bfloat16, dev)
+            engine = Engine(spec, tensors, dtype="bfloat16", max_tokens=B * (args.prompt + 256) + P + 64, max_seqs=B + 1,
+                            max_step_tokens=max(P, 2048), max_context=max(args.prompt + 256, P + 64), with_sampler=False)
+            del tensors
+            engine.warm_up()
+            V = engine.spec.vocab_size
+            prompt = rng.integers(0, V, size=P).tolist()
+
+            def prefill():
+                s = engine.open(1)
+                engine.step(s, [prompt], None)
+                engine.close(s)
+            for _ in range(W):
+                prefill()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(4):
+                prefill()
+            b.record()
+            torch.cuda.synchronize()
+            prefill_ms = a.elapsed_time(b) / 4
+            kp = _kernel_times(prefill)
+            slots = engine.open(B)
+            fill_cache(engine, slots, args.prompt)
+
+            def decode():
+                engine.step(slots, [[int(t)] for t in rng.integers(0, V, size=B)], None, borrow=True)
+            for _ in range(W + 3):
+                decode()
+            torch.cuda.synchronize()
+            a.record()
+            for _ in range(K):
+                decode()
+            b.record()
+            torch.cuda.synchronize()
+            decode_ms = a.elapsed_time(b) / K
+            kd = _kernel_times(decode)
+            engine.close(slots)
+            engine.check_errors()
+            wbytes = sum(int(np.prod(sp.shape)) * (2 if sp.kind == "matrix" else 4) for sp in spec.weight_specs()
+                         if not sp.name.startswith(("embed", "model.embed")))
+            result[size][model] = {"prefill_tokens": P, "prefill_ms": round(prefill_ms, 3),
+                                   "prefill_tok_s": round(P / prefill_ms * 1e3), "decode_batch": B,
+                                   "decode_context": args.prompt, "decode_ms": round(decode_ms, 4),
+                                   "decode_tok_s": round(B / decode_ms * 1e3), "weight_bytes": wbytes,
+                                   "kernels_prefill_us": kp, "kernels_decode_us": kd}
+            print(f"[bench] {size} {model}: prefill {prefill_ms:.2f} ms, decode {decode_ms * 1e3:.0f} us", file=sys.stderr, flush=True)
+            del engine
+            torch.cuda.empty_cache()
+    print(json.dumps({"only": "sugizen", "dtype": "bf16", "data": "synthetic", "peaks": peaks(), "clocks": clocks.stop(),
+                      "sizes": result}))
+    return 0
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -772,12 +900,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample", "attention", "peaks"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample", "attention", "peaks", "sugizen"],
                     help="a part of the run only (for profiling); the JSON line then holds that part. "
                          "timeline: every kernel of a decode step with its begin and end inside the graph "
                          "(timeline-prefill: of a prompt); "
                          "sample: the sampling kernel alone, option by option; attention: the prompt attention alone; "
-                         "peaks: this GPU's copy bandwidth and library bfloat16 product, the denominators' kind")
+                         "peaks: this GPU's copy bandwidth and library bfloat16 product, the denominators' kind; "
+                         "sugizen: prompt and decode throughput of the Sugizen design beside Qwen3 at equal layer sizes "
+                         "(two widths, eight layers), with every kernel's time in a prompt and in a decode step")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the decode step")
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="positions each sequence holds before the timed steps")
@@ -805,6 +935,8 @@ def main():
         return attention_times()
     if args.only == "peaks":
         return measured_peaks()
+    if args.only == "sugizen":
+        return sugizen_times(args)
     if args.config != "8b":
         return run_other(args)
     return run_ours(args)
