@@ -110,7 +110,9 @@ UB_API int ub_attn_simple(const void* q, long long q_stride, int act_dtype, cons
 //   V cache          = v                    (head size hd_v)
 // norm: RMS over the head with weight qw / kw (null: none); rotate: the first ``rd`` columns in pairs
 // (j, j + rd/2) by the token's position (cos, sin [positions, rd/2]; null: none).  k_off < 0: the layer
-// has no keys and values of its own and only its queries are made.  One warp a (token, head).
+// has no keys and values of its own and only its queries are made.  gate_out (optional, float32
+// [T, nh]) receives the nh columns from g_off on, summed over the parts: one gate a head for the
+// attention kernel.  One warp a (token, head).
 // ---------------------------------------------------------------------------------------
 template <typename TX, typename TQ, typename TC>
 __global__ void __launch_bounds__(128)
@@ -118,7 +120,7 @@ qkv_place_kernel(const TX* __restrict__ x, long long ldx, int n_parts, long long
                  TQ* __restrict__ q_out, long long ldq, const float* __restrict__ qw, const float* __restrict__ kw,
                  const float* __restrict__ cs, const float* __restrict__ sn, int rd, const int* __restrict__ tok_pos,
                  const int* __restrict__ tok_seq, TC* __restrict__ kc, TC* __restrict__ vc, PagedKV c, PagedKV cv,
-                 int n_tokens, int nh, float eps) {
+                 int n_tokens, int nh, float eps, int g_off, float* __restrict__ gate_out) {
     pdl_trigger();
     pdl_wait();
     const int units = nh + (k_off >= 0 ? 2 * c.n_kv_heads : 0);
@@ -142,6 +144,7 @@ qkv_place_kernel(const TX* __restrict__ x, long long ldx, int n_parts, long long
     const bool is_q = unit < nh;
     const int head = is_q ? unit : unit - nh;
     const int hd = c.head_dim;
+    if (is_q && gate_out && lane == 0) gate_out[t * nh + head] = at(g_off + head);
     const int c0 = (is_q ? q_off : k_off) + head * hd;
     const float* w = is_q ? qw : kw;
     float v[8];
@@ -190,7 +193,7 @@ UB_API int ub_qkv_place(const void* x, int x_dtype, long long ldx, int n_parts, 
                         int v_off, void* q_out, int q_dtype, long long ldq, const float* qw, const float* kw, const float* cs,
                         const float* sn, int rd, const int* tok_pos, const int* tok_seq, void* kcache, void* vcache,
                         int cache_dtype, const int* table, int pages_per_seq, int ring, int page, int n_tokens, int nh,
-                        int nkv, int hd, int hd_v, float eps, cudaStream_t st) {
+                        int nkv, int hd, int hd_v, float eps, int g_off, float* gate_out, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hd <= 0 || hd > 256 || hd_v <= 0 || nh <= 0 || nkv <= 0 || n_parts < 1 || (cs && (rd % 2 || rd < 2 || rd > hd)) ||
         ring % page != 0) return UB_ERR_ARG;
@@ -200,7 +203,7 @@ UB_API int ub_qkv_place(const void* x, int x_dtype, long long ldx, int n_parts, 
     const unsigned grid = (unsigned)((warps + 3) / 4);
     cudaError_t e;
 #define GO(TX, TQ, TC) e = ub_launch_dependent(qkv_place_kernel<TX, TQ, TC>, dim3(grid), dim3(128), 0, st, (const TX*)x, ldx, n_parts, \
-        part_stride, q_off, k_off, v_off, (TQ*)q_out, ldq, qw, kw, cs, sn, rd, tok_pos, tok_seq, (TC*)kcache, (TC*)vcache, c, cv, n_tokens, nh, eps)
+        part_stride, q_off, k_off, v_off, (TQ*)q_out, ldq, qw, kw, cs, sn, rd, tok_pos, tok_seq, (TC*)kcache, (TC*)vcache, c, cv, n_tokens, nh, eps, g_off, gate_out)
     if (x_dtype == UB_F32 && q_dtype == UB_F32 && cache_dtype == UB_F32) GO(float, float, float);
     else if (x_dtype == UB_F32 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) GO(float, __nv_bfloat16, __nv_bfloat16);
     else if (x_dtype == UB_BF16 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);

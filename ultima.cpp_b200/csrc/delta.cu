@@ -12,12 +12,13 @@
 //   delta_prepare      short convolution + SiLU of q, k, v; unit vectors; write strength; decay
 //   conv_state_update  the convolution's last inputs, carried to the next step
 //   delta_scan         the recurrence
-//   delta_finish       per-head RMS norm of o, weight, sigmoid output gate from a low-rank product
-// Everything is float32; the projections come in as float32 sums of the products.
+//   delta_finish       per-head RMS norm of o, weight, sigmoid output gate
+// Everything is float32; the projections come in as float32 sums of the products (for few tokens as the
+// partial sums of K slices, which the kernels add up as they read).
 #include "common.cuh"
+#include <stdlib.h>
 
 constexpr int MAX_TAPS = 16;
-constexpr int MAX_RANK = 256;
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
@@ -25,16 +26,23 @@ __device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log
 struct DeltaShape {
     int H, G, D, E;          // heads, q/k heads, key size, value size
     int taps;                // convolution length (the last tap is the current token's)
-    int rank_a, rank_g;      // inner sizes of the decay's and the gate's low-rank products
-    int q_off, k_off, v_off, b_off, a_off, g_off;   // columns of a projection row
+    int q_off, k_off, v_off, b_off;   // columns of a projection row
     long long ldp;           // row stride of the projections
+    int n_parts;             // the projection row is the sum of this many partial results ...
+    long long part_stride;   // ... this many elements apart
 };
+
+__device__ __forceinline__ float proj_at(const float* __restrict__ p, const DeltaShape& s, long long t, int c) {
+    float v = 0.f;
+    for (int i = 0; i < s.n_parts; ++i) v += p[i * s.part_stride + t * s.ldp + c];
+    return v;
+}
 
 // One warp a (token, unit); units of a token: G query heads, G key heads, H value heads (which also
 // make the head's write strength and decay).
 __global__ void __launch_bounds__(128)
 delta_prepare_kernel(const float* __restrict__ p, DeltaShape s, const float* __restrict__ conv_w,
-                     const float* __restrict__ conv_state, const float* __restrict__ a2,
+                     const float* __restrict__ conv_state, const float* __restrict__ dpre,
                      const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                      const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
                      const int* __restrict__ seq_slot, float* __restrict__ qn, float* __restrict__ kn,
@@ -57,7 +65,7 @@ delta_prepare_kernel(const float* __restrict__ p, DeltaShape s, const float* __r
         float acc = 0.f;
         for (int j = K; j >= 0; --j) {                 // oldest input first
             const float w = conv_w[(long long)c * s.taps + (s.taps - 1 - j)];
-            const float x = (r - j >= 0) ? p[(long long)(t - j) * s.ldp + c] : st[(long long)(K + r - j) * C + c];
+            const float x = (r - j >= 0) ? proj_at(p, s, t - j, c) : st[(long long)(K + r - j) * C + c];
             acc = fmaf(w, x, acc);
         }
         return acc * sigmoidf_(acc);
@@ -88,19 +96,16 @@ delta_prepare_kernel(const float* __restrict__ p, DeltaShape s, const float* __r
     const int h = unit - 2 * s.G;
     for (int e = lane; e < s.E; e += 32)
         vc[(long long)t * s.H * s.E + h * s.E + e] = conv_silu(s.v_off + h * s.E + e);
-    const float* row = p + (long long)t * s.ldp;
-    if (lane == 0) beta[(long long)t * s.H + h] = sigmoidf_(row[s.b_off + h]);
+    if (lane == 0) beta[(long long)t * s.H + h] = sigmoidf_(proj_at(p, s, t, s.b_off + h));
     const float rate = expf(a_log[h]);
     for (int d = lane; d < s.D; d += 32) {
-        const int c = h * s.D + d;
-        float a = dt_bias[c];
-        for (int k = 0; k < s.rank_a; ++k) a = fmaf(a2[(long long)c * s.rank_a + k], row[s.a_off + k], a);
-        dec[(long long)t * s.H * s.D + c] = expf(-rate * softplusf_(a));
+        const long long c = (long long)t * s.H * s.D + h * s.D + d;
+        dec[c] = expf(-rate * softplusf_(dpre[c] + dt_bias[h * s.D + d]));
     }
 }
 
 // One thread a (sequence, channel): the last taps - 1 inputs of what the state held followed by the step's.
-__global__ void conv_state_update_kernel(const float* __restrict__ p, long long ldp, float* __restrict__ conv_state,
+__global__ void conv_state_update_kernel(const float* __restrict__ p, DeltaShape s, float* __restrict__ conv_state,
                                          const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                                          int n_seqs, int C, int taps) {
     pdl_trigger();
@@ -114,25 +119,48 @@ __global__ void conv_state_update_kernel(const float* __restrict__ p, long long 
     float tmp[MAX_TAPS];
     for (int k = 0; k < K; ++k) {
         const int rel = n - K + k;
-        tmp[k] = rel >= 0 ? p[(long long)(first + rel) * ldp + c] : st[(long long)(K + rel) * C + c];
+        tmp[k] = rel >= 0 ? proj_at(p, s, first + rel, c) : st[(long long)(K + rel) * C + c];
     }
     for (int k = 0; k < K; ++k) st[(long long)k * C + c] = tmp[k];
 }
 
-// The recurrence.  A block takes 32 value channels of one head of one sequence; eight lanes hold one
-// column of S (lane p the key channels p, p + 8, ...), so a warp holds four columns and a dot product
-// over the key channels ends in three exchanges.  Tokens come through shared memory eight at a time.
-constexpr int SCAN_COLS = 32, SCAN_LANES = 8, SCAN_TOKENS = 8;
+// The recurrence.  A block of 128 threads takes 128 / LANES value channels of one head of one sequence;
+// LANES (8, 16 or 32) lanes hold one column of S, lane p the key channels of the float4 chunks p,
+// p + LANES, ...: the lanes of a column read consecutive bytes of shared memory in one instruction, and a
+// dot product over the key channels ends in log2(LANES) exchanges.  Tokens come through shared memory a
+// few at a time, the next few asked for (cp.async) while these are worked on.
+//
+// The kernel is bound by latency, not by bytes or arithmetic: a token's update depends on the one before
+// it through a chain of multiply, dot product, exchanges and update, and a warp issues in order.  The
+// read-out o = S^T q is off that chain: its partial sums go to shared memory and are added up once for
+// the tokens of a stage, and the loop over a full stage's tokens is unrolled.
 
-template <int R>
-__global__ void __launch_bounds__(SCAN_COLS * SCAN_LANES)
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
+// VEC: sizes are multiples of 4 and every array starts on a 16-byte boundary, so tokens are fetched in
+// 16-byte copies, each thread keeping the same one or two places of a token's row for the whole launch.
+template <int R, int SCAN_LANES, bool VEC>
+__global__ void __launch_bounds__(128)
 delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vc,
                   const float* __restrict__ beta, const float* __restrict__ dec, float* __restrict__ out,
                   float* __restrict__ S, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
                   int H, int G, int D, int E) {
+    static_assert(R % 4 == 0, "a lane holds whole float4 chunks");
+    constexpr int SCAN_COLS = 128 / SCAN_LANES;
     constexpr int DP = SCAN_LANES * R;
-    __shared__ float sq[SCAN_TOKENS][DP], sk[SCAN_TOKENS][DP], sa[SCAN_TOKENS][DP];
-    __shared__ float sv[SCAN_TOKENS][SCAN_COLS], sb[SCAN_TOKENS];
+    constexpr int NC = R / 4;                             // chunks a lane
+    constexpr int TT = DP <= 128 ? 8 : 4;                 // tokens a stage
+    __shared__ __align__(16) float sq[2][TT][DP], sk[2][TT][DP], sa[2][TT][DP];
+    __shared__ __align__(16) float sv[2][TT][SCAN_COLS];
+    __shared__ float sb[2][TT];
+    __shared__ float so[TT][128];                          // the read-out's partial sums, [token][lane of the column][column]
     pdl_trigger();
     pdl_wait();
     const int tid = threadIdx.x;
@@ -146,65 +174,143 @@ delta_scan_kernel(const float* __restrict__ qn, const float* __restrict__ kn, co
     float s[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int d = p + SCAN_LANES * i;
+        const int d = ((i >> 2) * SCAN_LANES + p) * 4 + (i & 3);
         s[i] = (d < D && j < E) ? Sh[(long long)d * E + j] : 0.f;
     }
-    for (int base = t0; base < t1; base += SCAN_TOKENS) {
-        const int n = min(SCAN_TOKENS, t1 - base);
-        __syncthreads();
-        for (int idx = tid; idx < n * DP; idx += blockDim.x) {
-            const int tt = idx / DP, d = idx % DP;
+    // columns past the sizes are constants that no copy ever touches
+    for (int idx = tid; idx < 2 * TT * DP; idx += blockDim.x) {
+        const int d = idx % DP;
+        if (d >= D) { (&sq[0][0][0])[idx] = 0.f; (&sk[0][0][0])[idx] = 0.f; (&sa[0][0][0])[idx] = 1.f; }
+    }
+    for (int idx = tid; idx < 2 * TT * SCAN_COLS; idx += blockDim.x)
+        if (blockIdx.x * SCAN_COLS + idx % SCAN_COLS >= E) (&sv[0][0][0])[idx] = 0.f;
+
+    // this thread's places in a token's [q | k | decay] row of 3 * D / 4 chunks (VEC)
+    int my_arr[2] = {-1, -1}, my_d[2] = {0, 0};
+    if (VEC) {
+        const int d4 = D >> 2;
+        for (int sl = 0; sl < 2; ++sl) {
+            const int c = tid + sl * (int)blockDim.x;
+            if (c < 3 * d4) { my_arr[sl] = c / d4; my_d[sl] = (c % d4) * 4; }
+        }
+    }
+    const float* qrow = qn + (long long)g * D;
+    const float* krow = kn + (long long)g * D;
+    const float* arow = dec + (long long)h * D;
+    const float* vrow = vc + (long long)h * E + blockIdx.x * SCAN_COLS;
+
+    auto fetch = [&](int base, int buf) {
+        const int n = min(TT, t1 - base);
+        if (VEC) {
+            for (int tt = 0; tt < n; ++tt) {
+                const long long t = base + tt;
+#pragma unroll
+                for (int sl = 0; sl < 2; ++sl) {
+                    const int d = my_d[sl];
+                    if (my_arr[sl] == 0) cp_async16(&sq[buf][tt][d], qrow + t * G * D + d);
+                    else if (my_arr[sl] == 1) cp_async16(&sk[buf][tt][d], krow + t * G * D + d);
+                    else if (my_arr[sl] == 2) cp_async16(&sa[buf][tt][d], arow + t * H * D + d);
+                }
+            }
+            if (tid < n * (SCAN_COLS / 4)) {
+                const int tt = tid / (SCAN_COLS / 4), c = (tid % (SCAN_COLS / 4)) * 4;
+                if (blockIdx.x * SCAN_COLS + c < E) cp_async16(&sv[buf][tt][c], vrow + (long long)(base + tt) * H * E + c);
+            }
+            if (tid >= 64 && tid < 64 + n) cp_async4(&sb[buf][tid - 64], beta + (long long)(base + tid - 64) * H + h);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            return;
+        }
+        for (int idx = tid; idx < n * D; idx += blockDim.x) {
+            const int tt = idx / D, d = idx % D;
             const long long t = base + tt;
-            const bool in = d < D;
-            sq[tt][d] = in ? qn[(t * G + g) * D + d] : 0.f;
-            sk[tt][d] = in ? kn[(t * G + g) * D + d] : 0.f;
-            sa[tt][d] = in ? dec[(t * H + h) * D + d] : 1.f;
+            cp_async4(&sq[buf][tt][d], qn + (t * G + g) * D + d);
+            cp_async4(&sk[buf][tt][d], kn + (t * G + g) * D + d);
+            cp_async4(&sa[buf][tt][d], dec + (t * H + h) * D + d);
         }
         for (int idx = tid; idx < n * SCAN_COLS; idx += blockDim.x) {
             const int tt = idx / SCAN_COLS, c = idx % SCAN_COLS;
             const int jj = blockIdx.x * SCAN_COLS + c;
-            sv[tt][c] = jj < E ? vc[((long long)(base + tt) * H + h) * E + jj] : 0.f;
+            if (jj < E) cp_async4(&sv[buf][tt][c], vc + ((long long)(base + tt) * H + h) * E + jj);
         }
-        if (tid < n) sb[tid] = beta[(long long)(base + tid) * H + h];
+        if (tid < n) cp_async4(&sb[buf][tid], beta + (long long)(base + tid) * H + h);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+
+    fetch(t0, 0);
+    int buf = 0;
+    for (int base = t0; base < t1; base += TT, buf ^= 1) {
+        const int n = min(TT, t1 - base);
+        if (base + TT < t1) {
+            fetch(base + TT, buf ^ 1);                    // (that buffer's readers passed the barrier at the end of the last round)
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
         __syncthreads();
-        for (int tt = 0; tt < n; ++tt) {
-            float dot = 0.f;
+        auto token = [&](int tt) {
+            const float4* a4 = reinterpret_cast<const float4*>(sa[buf][tt]);
+            const float4* k4 = reinterpret_cast<const float4*>(sk[buf][tt]);
+            const float4* q4 = reinterpret_cast<const float4*>(sq[buf][tt]);
+            float4 kk[NC];
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                const int d = p + SCAN_LANES * i;
-                s[i] *= sa[tt][d];
-                dot = fmaf(s[i], sk[tt][d], dot);
+            for (int c = 0; c < NC; ++c) {
+                const float4 a = a4[c * SCAN_LANES + p];
+                kk[c] = k4[c * SCAN_LANES + p];
+                s[4 * c + 0] *= a.x; s[4 * c + 1] *= a.y; s[4 * c + 2] *= a.z; s[4 * c + 3] *= a.w;
+                part[0] = fmaf(s[4 * c + 0], kk[c].x, part[0]);
+                part[1] = fmaf(s[4 * c + 1], kk[c].y, part[1]);
+                part[2] = fmaf(s[4 * c + 2], kk[c].z, part[2]);
+                part[3] = fmaf(s[4 * c + 3], kk[c].w, part[3]);
             }
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-            const float u = sb[tt] * (sv[tt][col] - dot);
+            float dot = (part[0] + part[1]) + (part[2] + part[3]);
+#pragma unroll
+            for (int w = 1; w < SCAN_LANES; w <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, w);
+            const float u = sb[buf][tt] * (sv[buf][tt][col] - dot);
+            float op[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < NC; ++c) {
+                const float4 q = q4[c * SCAN_LANES + p];
+                s[4 * c + 0] = fmaf(kk[c].x, u, s[4 * c + 0]);
+                s[4 * c + 1] = fmaf(kk[c].y, u, s[4 * c + 1]);
+                s[4 * c + 2] = fmaf(kk[c].z, u, s[4 * c + 2]);
+                s[4 * c + 3] = fmaf(kk[c].w, u, s[4 * c + 3]);
+                op[0] = fmaf(s[4 * c + 0], q.x, op[0]);
+                op[1] = fmaf(s[4 * c + 1], q.y, op[1]);
+                op[2] = fmaf(s[4 * c + 2], q.z, op[2]);
+                op[3] = fmaf(s[4 * c + 3], q.w, op[3]);
+            }
+            so[tt][p * SCAN_COLS + col] = (op[0] + op[1]) + (op[2] + op[3]);      // summed over the lanes behind the loop
+        };
+        if (n == TT) {
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt) token(tt);
+        } else {
+            for (int tt = 0; tt < n; ++tt) token(tt);
+        }
+        __syncthreads();
+        if (tid < n * SCAN_COLS) {                            // one thread a (token, column): the lanes' partial sums in lane order
+            const int tt = tid / SCAN_COLS, c = tid % SCAN_COLS;
+            const int jj = blockIdx.x * SCAN_COLS + c;
             float o = 0.f;
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                const int d = p + SCAN_LANES * i;
-                s[i] = fmaf(sk[tt][d], u, s[i]);
-                o = fmaf(s[i], sq[tt][d], o);
-            }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            if (p == 0 && j < E) out[((long long)(base + tt) * H + h) * E + j] = o;
+            for (int l = 0; l < SCAN_LANES; ++l) o += so[tt][l * SCAN_COLS + c];
+            if (jj < E) out[((long long)(base + tt) * H + h) * E + jj] = o;
         }
+        __syncthreads();                                  // this buffer is asked for again in the next round
     }
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int d = p + SCAN_LANES * i;
+        const int d = ((i >> 2) * SCAN_LANES + p) * 4 + (i & 3);
         if (d < D && j < E) Sh[(long long)d * E + j] = s[i];
     }
 }
 
-// One warp a (token, head): o / rms(o) * w * sigmoid(g2 (g1 h)), g1 h being columns of the projection row.
+// One warp a (token, head): o / rms(o) * w * sigmoid(z), z [T, H * E] the gate's sums.
 template <typename TO>
 __global__ void __launch_bounds__(128)
-delta_finish_kernel(const float* __restrict__ o, const float* __restrict__ p, long long ldp, int g_off, int rank_g,
-                    const float* __restrict__ g2, const float* __restrict__ w, TO* __restrict__ out,
-                    int n_tokens, int H, int E, float eps) {
+delta_finish_kernel(const float* __restrict__ o, const float* __restrict__ z, const float* __restrict__ w,
+                    TO* __restrict__ out, int n_tokens, int H, int E, float eps) {
     pdl_trigger();
     pdl_wait();
     const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -217,79 +323,89 @@ delta_finish_kernel(const float* __restrict__ o, const float* __restrict__ p, lo
     for (int e = lane; e < E; e += 32) { const float v = orow[e]; ss += v * v; }
     ss = warp_sum(ss);
     const float inv = inv_rms(ss, (float)E, eps);
-    const float* low = p + t * ldp + g_off;
-    for (int e = lane; e < E; e += 32) {
-        const int c = h * E + e;
-        float z = 0.f;
-        for (int k = 0; k < rank_g; ++k) z = fmaf(g2[(long long)c * rank_g + k], low[k], z);
-        out[(t * H + h) * E + e] = from_f32<TO>(orow[e] * inv * w[e] * sigmoidf_(z));
-    }
+    const float* zrow = z + (t * H + h) * E;
+    for (int e = lane; e < E; e += 32)
+        out[(t * H + h) * E + e] = from_f32<TO>(orow[e] * inv * w[e] * sigmoidf_(zrow[e]));
 }
 
 // ---------------------------------------------------------------------------------------
-// shape: [H, G, D, E, taps, rank_a, rank_g, q_off, k_off, v_off, b_off, a_off, g_off] (13 ints)
-static int read_shape(const int* shape, long long ldp, DeltaShape& s) {
+// shape: [H, G, D, E, taps, q_off, k_off, v_off, b_off] (9 ints)
+static int read_shape(const int* shape, long long ldp, int n_parts, long long part_stride, DeltaShape& s) {
     s.H = shape[0]; s.G = shape[1]; s.D = shape[2]; s.E = shape[3]; s.taps = shape[4];
-    s.rank_a = shape[5]; s.rank_g = shape[6];
-    s.q_off = shape[7]; s.k_off = shape[8]; s.v_off = shape[9]; s.b_off = shape[10]; s.a_off = shape[11]; s.g_off = shape[12];
-    s.ldp = ldp;
+    s.q_off = shape[5]; s.k_off = shape[6]; s.v_off = shape[7]; s.b_off = shape[8];
+    s.ldp = ldp; s.n_parts = n_parts; s.part_stride = part_stride;
     if (s.H <= 0 || s.G <= 0 || s.H % s.G || s.D <= 0 || s.D > 256 || s.E <= 0 || s.taps < 1 || s.taps > MAX_TAPS ||
-        s.rank_a < 1 || s.rank_a > MAX_RANK || s.rank_g < 1 || s.rank_g > MAX_RANK || s.H > 65535) return UB_ERR_ARG;
+        s.H > 65535 || n_parts < 1) return UB_ERR_ARG;
     // the convolution's state is indexed by projection column: q, k, v are the row's first columns
     if (s.q_off != 0 || s.k_off != s.G * s.D || s.v_off != 2 * s.G * s.D) return UB_ERR_ARG;
     return 0;
 }
 
-UB_API int ub_delta_prepare(const float* p, long long ldp, const int* shape, const float* conv_w, const float* conv_state,
-                            const float* a2, const float* dt_bias, const float* a_log, const int* tok_seq,
+UB_API int ub_delta_prepare(const float* p, long long ldp, int n_parts, long long part_stride, const int* shape,
+                            const float* conv_w, const float* conv_state, const float* dpre, const float* dt_bias,
+                            const float* a_log, const int* tok_seq,
                             const int* seq_start, const int* seq_slot, float* qn, float* kn, float* vc, float* beta,
                             float* dec, int n_tokens, float unit_eps, float q_scale, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     DeltaShape s;
-    if (int rc = read_shape(shape, ldp, s)) return rc;
+    if (int rc = read_shape(shape, ldp, n_parts, part_stride, s)) return rc;
     const long long warps = (long long)n_tokens * (2 * s.G + s.H);
     const unsigned grid = (unsigned)((warps + 3) / 4);
-    return (int)ub_launch_dependent(delta_prepare_kernel, dim3(grid), dim3(128), 0, st, p, s, conv_w, conv_state, a2, dt_bias,
+    return (int)ub_launch_dependent(delta_prepare_kernel, dim3(grid), dim3(128), 0, st, p, s, conv_w, conv_state, dpre, dt_bias,
                                     a_log, tok_seq, seq_start, seq_slot, qn, kn, vc, beta, dec, n_tokens, unit_eps, q_scale);
 }
 
-UB_API int ub_conv_state_update(const float* p, long long ldp, float* conv_state, const int* seq_start, const int* seq_slot,
-                                int n_seqs, int C, int taps, cudaStream_t st) {
+UB_API int ub_conv_state_update(const float* p, long long ldp, int n_parts, long long part_stride, float* conv_state,
+                                const int* seq_start, const int* seq_slot, int n_seqs, int C, int taps, cudaStream_t st) {
     if (n_seqs <= 0 || taps <= 1) return 0;
-    if (taps > MAX_TAPS) return UB_ERR_ARG;
+    if (taps > MAX_TAPS || n_parts < 1) return UB_ERR_ARG;
+    DeltaShape s = {};
+    s.ldp = ldp; s.n_parts = n_parts; s.part_stride = part_stride;
     const long long n = (long long)n_seqs * C;
-    return (int)ub_launch_dependent(conv_state_update_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, st, p, ldp,
+    return (int)ub_launch_dependent(conv_state_update_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, st, p, s,
                                     conv_state, seq_start, seq_slot, n_seqs, C, taps);
 }
 
 UB_API int ub_delta_scan(const float* qn, const float* kn, const float* vc, const float* beta, const float* dec, float* out,
                          float* S, const int* seq_start, const int* seq_slot, int n_seqs, int H, int G, int D, int E,
-                         cudaStream_t st) {
+                         int sm_count, cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || D > 256 || E <= 0 || H > 65535 || n_seqs > 65535) return UB_ERR_ARG;
-    const dim3 grid((E + SCAN_COLS - 1) / SCAN_COLS, H, n_seqs), block(SCAN_COLS * SCAN_LANES);
-    cudaError_t e;
-#define GO(R) e = ub_launch_dependent(delta_scan_kernel<R>, grid, block, 0, st, qn, kn, vc, beta, dec, out, S, seq_start, seq_slot, H, G, D, E)
-    if (D <= 16) GO(2);
-    else if (D <= 32) GO(4);
-    else if (D <= 64) GO(8);
-    else if (D <= 128) GO(16);
-    else GO(32);
+    const bool vec = D % 4 == 0 && E % 4 == 0 && (((uintptr_t)qn | (uintptr_t)kn | (uintptr_t)vc | (uintptr_t)dec) & 15) == 0;
+    // lanes a column: eight, and more (fewer values and a shorter chain a thread) only while the launch still has
+    // no more than about one warp for every scheduler and every lane gets a whole float4 chunk; measured at 2,048
+    // tokens, 16 heads, sizes of 128: 346 / 372 / 405 ns a token with 8 / 16 / 32 lanes, at sizes of 64: 322 / 296
+    static const int forced = getenv("ULTIMA_SCAN_LANES") ? atoi(getenv("ULTIMA_SCAN_LANES")) : 0;    // for measurements
+    const long long budget = 4LL * (sm_count > 0 ? sm_count : 148);
+    auto warps_with = [&](int l) { return (long long)n_seqs * H * ((E * l + 127) / 128) * 4; };
+    int lanes = 8;
+    while (lanes < 32 && lanes * 2 * 4 <= ((D + 3) / 4) * 4 && warps_with(lanes * 2) <= budget) lanes <<= 1;
+    if (forced == 8 || forced == 16 || forced == 32) lanes = forced;
+    while (lanes > 8 && lanes * 4 > ((D + 3) / 4) * 4) lanes >>= 1;
+    const int cols = 128 / lanes;
+    const dim3 grid((E + cols - 1) / cols, H, n_seqs), block(128);
+    const int per_lane = (D + lanes - 1) / lanes;          // key channels a lane, rounded up to whole chunks
+    const int R = per_lane <= 4 ? 4 : per_lane <= 8 ? 8 : per_lane <= 16 ? 16 : 32;
+    cudaError_t e = cudaErrorInvalidValue;
+#define GO(RR, LL) e = vec ? ub_launch_dependent(delta_scan_kernel<RR, LL, true>, grid, block, 0, st, qn, kn, vc, beta, dec, out, S, seq_start, seq_slot, H, G, D, E) \
+                           : ub_launch_dependent(delta_scan_kernel<RR, LL, false>, grid, block, 0, st, qn, kn, vc, beta, dec, out, S, seq_start, seq_slot, H, G, D, E)
+    if (lanes == 32) { if (R == 4) GO(4, 32); else if (R == 8) GO(8, 32); else return UB_ERR_ARG; }
+    else if (lanes == 16) { if (R == 4) GO(4, 16); else if (R == 8) GO(8, 16); else if (R == 16) GO(16, 16); else return UB_ERR_ARG; }
+    else { if (R == 4) GO(4, 8); else if (R == 8) GO(8, 8); else if (R == 16) GO(16, 8); else GO(32, 8); }
 #undef GO
     return (int)e;
 }
 
-UB_API int ub_delta_finish(const float* o, const float* p, long long ldp, int g_off, int rank_g, const float* g2,
-                           const float* w, void* out, int out_dtype, int n_tokens, int H, int E, float eps, cudaStream_t st) {
+UB_API int ub_delta_finish(const float* o, const float* z, const float* w, void* out, int out_dtype, int n_tokens, int H,
+                           int E, float eps, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
-    if (rank_g < 1 || rank_g > MAX_RANK) return UB_ERR_ARG;
     const long long warps = (long long)n_tokens * H;
     const unsigned grid = (unsigned)((warps + 3) / 4);
     cudaError_t e;
     if (out_dtype == UB_F32)
-        e = ub_launch_dependent(delta_finish_kernel<float>, dim3(grid), dim3(128), 0, st, o, p, ldp, g_off, rank_g, g2, w, (float*)out, n_tokens, H, E, eps);
+        e = ub_launch_dependent(delta_finish_kernel<float>, dim3(grid), dim3(128), 0, st, o, z, w, (float*)out, n_tokens, H, E, eps);
     else if (out_dtype == UB_BF16)
-        e = ub_launch_dependent(delta_finish_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, o, p, ldp, g_off, rank_g, g2, w, (__nv_bfloat16*)out, n_tokens, H, E, eps);
+        e = ub_launch_dependent(delta_finish_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, o, z, w, (__nv_bfloat16*)out, n_tokens, H, E, eps);
     else return UB_ERR_UNSUPPORTED;
     return (int)e;
 }

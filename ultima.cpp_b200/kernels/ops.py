@@ -113,11 +113,11 @@ def _declare(lib, source: str) -> None:
         "gemm_simt.cu": {"ub_gemm_simt": [P, I, P, P, I, P, I, I, I, I, L, L, L, I, P]},
         "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, L, P],
                            "ub_qkv_place": [P, I, L, I, L, I, I, I, P, I, L, P, P, P, P, I, P, P, P, P, I, P, I, I, I, I, I,
-                                            I, I, I, F, P]},
-        "delta.cu": {"ub_delta_prepare": [P, L, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, F, F, P],
-                     "ub_conv_state_update": [P, L, P, P, P, I, I, I, P],
-                     "ub_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, P],
-                     "ub_delta_finish": [P, P, L, I, I, P, P, P, I, I, I, I, F, P]},
+                                            I, I, I, F, I, P, P]},
+        "delta.cu": {"ub_delta_prepare": [P, L, I, L, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, F, F, P],
+                     "ub_conv_state_update": [P, L, I, L, P, P, P, I, I, I, P],
+                     "ub_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+                     "ub_delta_finish": [P, P, P, P, I, I, I, I, F, P]},
         "sampling.cu": {"ub_sample": [P, L, P, I, I, P, P, P, P, P, U, P, P, I, P], "ub_sample_params_size": []},
     }.get(source, {})
     for name, args in sigs.items():
@@ -326,10 +326,11 @@ def attn_simple(q, k_cache, v_cache, out, tok_pos, tok_seq, table, ring, page, n
 
 
 def qkv_place(x, q_off, k_off, v_off, q_out, q_weight, k_weight, cos, sin, rotary_dim, tok_pos, tok_seq, k_cache,
-              v_cache, table, ring, page, n_heads, n_kv_heads, head_dim, v_head_dim, eps):
+              v_cache, table, ring, page, n_heads, n_kv_heads, head_dim, v_head_dim, eps, g_off=None, gate_out=None):
     """Queries normed and rotated into ``q_out`` [T, heads * head size]; keys (normed, rotated) and values into the
     paged cache.  x: projection rows [T, N] or [parts, T, N] (summed), with the query heads from column q_off, the
-    key heads from k_off and the value heads from v_off; k_off None: queries only."""
+    key heads from k_off and the value heads from v_off; k_off None: queries only.  ``gate_out`` (float32
+    [T, heads], contiguous) receives the ``heads`` columns from ``g_off`` on (summed over the parts)."""
     _need_cuda(x, q_out, k_cache, v_cache, table)
     if x.dim() == 3:
         n_parts, T, part_stride, ldx = x.shape[0], x.shape[1], x.stride(0), x.stride(1)
@@ -344,55 +345,75 @@ def qkv_place(x, q_off, k_off, v_off, q_out, q_weight, k_weight, cos, sin, rotar
     rd = int(rotary_dim or 0)
     if cos is not None:
         assert cos.shape[1] == rd // 2 and sin.shape == cos.shape
+    if gate_out is not None:
+        assert gate_out.dtype == torch.float32 and gate_out.is_contiguous() and gate_out.shape == (T, n_heads)
+        assert g_off is not None
     _check(_lib("attn_simple.cu").ub_qkv_place(
         _ptr(x), _code(x), ldx, n_parts, part_stride, int(q_off), -1 if k_off is None else int(k_off),
         -1 if v_off is None else int(v_off), _ptr(q_out), _code(q_out), q_out.stride(0), _ptr(q_weight), _ptr(k_weight),
         _ptr(cos), _ptr(sin), rd, _ptr(tok_pos), _ptr(tok_seq), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(table),
-        table.shape[1], ring, page, T, n_heads, n_kv_heads, head_dim, int(v_head_dim), float(eps), _stream()), "qkv_place")
+        table.shape[1], ring, page, T, n_heads, n_kv_heads, head_dim, int(v_head_dim), float(eps), int(g_off or 0),
+        _ptr(gate_out), _stream()), "qkv_place")
 
 
 # ---------------------------------------------------------------------------------------
 # the gated delta-rule mixer (csrc/delta.cu)
-def delta_shape(H, G, D, E, taps, rank_a, rank_g, offs):
-    """The shape record the delta kernels read: sizes and the columns of a projection row
-    (offs = (q, k, v, b, a, g) first columns)."""
+def delta_shape(H, G, D, E, taps, offs):
+    """The shape record the delta kernels read: sizes and the first columns of q, k, v and the write
+    strength in a projection row."""
     from ctypes import c_int as _ci
-    vals = [H, G, D, E, taps, rank_a, rank_g] + [int(o) for o in offs]
+    vals = [H, G, D, E, taps] + [int(o) for o in offs]
     return (_ci * len(vals))(*vals)
 
 
-def delta_prepare(p, shape, conv_w, conv_state, a2, dt_bias, a_log, batch, qn, kn, vc, beta, dec, unit_eps, q_scale):
-    _need_cuda(p, conv_w, conv_state, a2, qn, kn, vc, beta, dec)
-    assert p.dtype == torch.float32 and p.stride(1) == 1
-    for t in (conv_w, conv_state, a2, dt_bias, a_log, qn, kn, vc, beta, dec):
+def _parts_of(p):
+    """(rows, row stride, parts, part stride) of projections [T, N] or [parts, T, N] (summed over parts)."""
+    if p.dim() == 3:
+        assert p.stride(2) == 1
+        return p.shape[1], p.stride(1), p.shape[0], p.stride(0)
+    assert p.stride(1) == 1
+    return p.shape[0], p.stride(0), 1, 0
+
+
+def delta_prepare(p, shape, conv_w, conv_state, decay_pre, dt_bias, a_log, batch, qn, kn, vc, beta, dec, unit_eps, q_scale):
+    """p: the projections [q | k | v | write strength] in float32; decay_pre [T, heads * key size]: the decay's
+    sums before the bias.  Fills qn, kn (unit vectors), vc, beta and dec."""
+    _need_cuda(p, conv_w, conv_state, decay_pre, qn, kn, vc, beta, dec)
+    assert p.dtype == torch.float32
+    T, ldp, n_parts, part_stride = _parts_of(p)
+    for t in (conv_w, conv_state, decay_pre, dt_bias, a_log, qn, kn, vc, beta, dec):
         assert t.dtype == torch.float32 and t.is_contiguous()
     _check(_lib("delta.cu").ub_delta_prepare(
-        _ptr(p), p.stride(0), shape, _ptr(conv_w), _ptr(conv_state), _ptr(a2), _ptr(dt_bias), _ptr(a_log),
-        _ptr(batch.tok_seq), _ptr(batch.seq_start), _ptr(batch.seq_slot), _ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta),
-        _ptr(dec), p.shape[0], float(unit_eps), float(q_scale), _stream()), "delta_prepare")
+        _ptr(p), ldp, n_parts, part_stride, shape, _ptr(conv_w), _ptr(conv_state), _ptr(decay_pre), _ptr(dt_bias),
+        _ptr(a_log), _ptr(batch.tok_seq), _ptr(batch.seq_start), _ptr(batch.seq_slot), _ptr(qn), _ptr(kn), _ptr(vc),
+        _ptr(beta), _ptr(dec), T, float(unit_eps), float(q_scale), _stream()), "delta_prepare")
 
 
 def conv_state_update(p, conv_state, batch, n_channels, taps):
     _need_cuda(p, conv_state)
     assert p.dtype == torch.float32 and conv_state.dtype == torch.float32 and conv_state.is_contiguous()
-    _check(_lib("delta.cu").ub_conv_state_update(_ptr(p), p.stride(0), _ptr(conv_state), _ptr(batch.seq_start),
-                                                 _ptr(batch.seq_slot), batch.n_seqs, n_channels, taps, _stream()),
-           "conv_state_update")
+    _, ldp, n_parts, part_stride = _parts_of(p)
+    _check(_lib("delta.cu").ub_conv_state_update(_ptr(p), ldp, n_parts, part_stride, _ptr(conv_state),
+                                                 _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seqs, n_channels,
+                                                 taps, _stream()), "conv_state_update")
 
 
 def delta_scan(qn, kn, vc, beta, dec, out, state, batch, H, G, D, E):
     _need_cuda(qn, kn, vc, beta, dec, out, state)
     assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, D, E)
     _check(_lib("delta.cu").ub_delta_scan(_ptr(qn), _ptr(kn), _ptr(vc), _ptr(beta), _ptr(dec), _ptr(out), _ptr(state),
-                                          _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seqs, H, G, D, E, _stream()),
+                                          _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seqs, H, G, D, E, sm_count(),
+                                          _stream()),
            "delta_scan")
 
 
-def delta_finish(o, p, g_off, rank_g, g2, weight, out, H, E, eps):
-    _need_cuda(o, p, g2, weight, out)
-    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and g2.dtype == torch.float32
-    _check(_lib("delta.cu").ub_delta_finish(_ptr(o), _ptr(p), p.stride(0), int(g_off), int(rank_g), _ptr(g2), _ptr(weight),
-                                            _ptr(out), _code(out), o.shape[0], H, E, float(eps), _stream()), "delta_finish")
+def delta_finish(o, gate_pre, weight, out, H, E, eps):
+    """out = o / rms(o) * weight * sigmoid(gate_pre), head by head; o, gate_pre float32 [T, H * E]."""
+    _need_cuda(o, gate_pre, weight, out)
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous()
+    assert gate_pre.dtype == torch.float32 and gate_pre.is_contiguous() and gate_pre.shape == o.shape
+    _check(_lib("delta.cu").ub_delta_finish(_ptr(o), _ptr(gate_pre), _ptr(weight), _ptr(out), _code(out), o.shape[0], H, E,
+                                            float(eps), _stream()), "delta_finish")
 
 
 # ---------------------------------------------------------------------------------------

@@ -136,17 +136,19 @@ class Attention(Mixer):
             raise ValueError("attention: a layer without keys and values of its own must read another run's "
                              "cache, and one with them must own its cache")
         rot = self.position.rotation() if self.position is not None else None
-        x = rt.arena.alloc((T, self.wqkv.shape[0]), torch.float32)
-        rt.matmul(h, self.wqkv, x)
+        x = rt.matmul_parts(h, self.wqkv)            # few tokens: K in slices, summed by the placement kernel
+        if x is None:
+            x = rt.arena.alloc((T, self.wqkv.shape[0]), torch.float32)
+            rt.matmul(h, self.wqkv, x)
         q = rt.arena.alloc((T, self.q_width), rt.dtype)
         k_off = self.q_width if self.own_kv else None
         v_off = self.q_width + self.kv_width if self.own_kv else None
         g_off = self.q_width + (self.kv_width + self.v_width if self.own_kv else 0)
+        gate = rt.arena.alloc((T, self.nh), torch.float32) if self.head_gate else None
         rt.launches += 1
         ops.qkv_place(x, 0, k_off, v_off, q, self.q_norm, self.k_norm, rot.cos if rot else None,
                       rot.sin if rot else None, rot.dim if rot else 0, batch.tok_pos, batch.tok_seq, kv.k, kv.v,
-                      kv.table, kv.ring, kv.page, self.nh, self.nkv, self.hd, self.hdv, self.eps)
-        gate = x[:, g_off:g_off + self.nh] if self.head_gate else None
+                      kv.table, kv.ring, kv.page, self.nh, self.nkv, self.hd, self.hdv, self.eps, g_off, gate)
         o = rt.arena.alloc((T, self.o_width), rt.dtype)
         if self._fast_attention() and rt.attention_fast(q, kv, o, batch, self.nh, self.nkv, self.hd, self.scale,
                                                         self.block):

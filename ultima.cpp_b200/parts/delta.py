@@ -25,8 +25,10 @@ class GatedDelta(Mixer):
     stream the mixer is handed.  The convolution's last ``conv - 1`` inputs are state too.
 
     Everything between the projections and the output projection is float32.  The projections that
-    read the mixer's input run as one product [q | k | v | b | decay_down | gate_down]; the two
-    low-rank up-projections are folded into the kernels that use their results.
+    read the mixer's input run as two products, [q | k | v | b] with float32 results (for few tokens in
+    K slices that the next kernel adds up) and [decay_down | gate_down] in the activation type, which
+    the two up-projections then take as their input (each padded to a multiple of 8 columns with zero
+    weights, so that both are aligned operands of the tensor-core product).
     """
 
     graph_safe = True
@@ -45,8 +47,8 @@ class GatedDelta(Mixer):
             raise ValueError(f"gated_delta: a convolution of {self.conv} taps is not one the kernels take (1 to 16)")
         if self.hd > 256:
             raise ValueError(f"gated_delta: key size {self.hd} is more than the scan kernel holds (256)")
-        if not (1 <= self.decay_rank <= 256 and 1 <= self.gate_rank <= 256):
-            raise ValueError("gated_delta: the low-rank products take inner sizes of 1 to 256")
+        if self.decay_rank < 1 or self.gate_rank < 1:
+            raise ValueError("gated_delta: the low-rank products need inner sizes of at least 1")
 
     def weight_specs(self):
         W, V = WeightSpec, "vector"
@@ -57,10 +59,10 @@ class GatedDelta(Mixer):
                 W("a_log", (self.nh,), V, ("normal", 0.5)),
                 W("o_norm.weight", (self.hdv,), V, ("one_plus_normal", 0.05)),
                 W("decay_down.weight", (self.decay_rank, self.width)),
-                W("decay_up.weight", (self.nh * self.hd, self.decay_rank), V, ("normal", 0.1)),
+                W("decay_up.weight", (self.nh * self.hd, self.decay_rank), "matrix", ("normal", 0.1)),
                 W("dt_bias", (self.nh * self.hd,), V, ("normal", 0.5)),
                 W("gate_down.weight", (self.gate_rank, self.width)),
-                W("gate_up.weight", (self.v_width, self.gate_rank), V, ("normal", 0.1)),
+                W("gate_up.weight", (self.v_width, self.gate_rank), "matrix", ("normal", 0.1)),
                 W("o_proj.weight", (self.width, self.v_width))]
 
     def cache_need(self):
@@ -71,30 +73,45 @@ class GatedDelta(Mixer):
         return [("delta.cu", ())]
 
     def bind(self, tensors, rt):
-        ws = [tensors[n + ".weight"] for n in ("q_proj", "k_proj", "v_proj", "b_proj", "decay_down", "gate_down")]
+        ws = [tensors[n + ".weight"] for n in ("q_proj", "k_proj", "v_proj", "b_proj", "decay_down", "gate_down",
+                                               "decay_up", "gate_up")]
         if len({w.dtype for w in ws}) != 1:
-            raise ValueError("gated_delta: the projections of the mixer's input must share one element type")
-        self.w_in = torch.cat(ws, dim=0).contiguous()
+            raise ValueError("gated_delta: the projections must share one element type")
+        self.w_in = torch.cat(ws[:4], dim=0).contiguous()
         self.b_off = self.channels
-        self.a_off = self.b_off + self.nh
-        self.g_off = self.a_off + self.decay_rank
+
+        def padded(w, rows, cols):
+            out = torch.zeros((rows, cols), dtype=w.dtype, device=w.device)
+            out[:w.shape[0], :w.shape[1]] = w
+            return out
+        ra, rg = -(-self.decay_rank // 8) * 8, -(-self.gate_rank // 8) * 8
+        self.low_split = ra
+        self.w_low = torch.cat([padded(ws[4], ra, self.width), padded(ws[5], rg, self.width)], dim=0).contiguous()
+        self.decay_up = padded(ws[6], ws[6].shape[0], ra).contiguous()
+        self.gate_up = padded(ws[7], ws[7].shape[0], rg).contiguous()
         self.conv_w = torch.cat([tensors[n].float() for n in ("q_conv.weight", "k_conv.weight", "v_conv.weight")],
                                 dim=0).contiguous()
-        self.decay_up = tensors["decay_up.weight"].float().contiguous()
-        self.gate_up = tensors["gate_up.weight"].float().contiguous()
         self.dt_bias = tensors["dt_bias"].float().contiguous()
         self.a_log = tensors["a_log"].float().contiguous()
         self.o_norm = tensors["o_norm.weight"].float().contiguous()
         self.wo = tensors["o_proj.weight"].contiguous()
-        self.shape = ops.delta_shape(self.nh, self.nkv, self.hd, self.hdv, self.conv, self.decay_rank, self.gate_rank,
-                                     (0, self.qk_width, 2 * self.qk_width, self.b_off, self.a_off, self.g_off))
+        self.shape = ops.delta_shape(self.nh, self.nkv, self.hd, self.hdv, self.conv,
+                                     (0, self.qk_width, 2 * self.qk_width, self.b_off))
 
     def forward(self, h, residual, batch, cache, rt):
         T = h.shape[0]
         S, conv_state = cache.states
         f32 = torch.float32
-        p = rt.arena.alloc((T, self.w_in.shape[0]), f32)
-        rt.matmul(h, self.w_in, p)
+        p = rt.matmul_parts(h, self.w_in)             # few tokens: K in slices, summed by the kernels that read them
+        if p is None:
+            p = rt.arena.alloc((T, self.w_in.shape[0]), f32)
+            rt.matmul(h, self.w_in, p)
+        low = rt.arena.alloc((T, self.w_low.shape[0]), rt.dtype)
+        rt.matmul(h, self.w_low, low)
+        decay_pre = rt.arena.alloc((T, self.nh * self.hd), f32)
+        rt.matmul(low[:, :self.low_split], self.decay_up, decay_pre)
+        gate_pre = rt.arena.alloc((T, self.v_width), f32)
+        rt.matmul(low[:, self.low_split:], self.gate_up, gate_pre)
         qn = rt.arena.alloc((T, self.qk_width), f32)
         kn = rt.arena.alloc((T, self.qk_width), f32)
         vc = rt.arena.alloc((T, self.v_width), f32)
@@ -103,9 +120,9 @@ class GatedDelta(Mixer):
         o = rt.arena.alloc((T, self.v_width), f32)
         oa = rt.arena.alloc((T, self.v_width), rt.dtype)
         rt.launches += 4
-        ops.delta_prepare(p, self.shape, self.conv_w, conv_state, self.decay_up, self.dt_bias, self.a_log, batch,
+        ops.delta_prepare(p, self.shape, self.conv_w, conv_state, decay_pre, self.dt_bias, self.a_log, batch,
                           qn, kn, vc, beta, dec, self.unit_eps, self.hd ** -0.5)
         ops.conv_state_update(p, conv_state, batch, self.channels, self.conv)
         ops.delta_scan(qn, kn, vc, beta, dec, o, S, batch, self.nh, self.nkv, self.hd, self.hdv)
-        ops.delta_finish(o, p, self.g_off, self.gate_rank, self.gate_up, self.o_norm, oa, self.nh, self.hdv, self.eps)
+        ops.delta_finish(o, gate_pre, self.o_norm, oa, self.nh, self.hdv, self.eps)
         rt.matmul(oa, self.wo, residual, ops.EPI_ADD)
