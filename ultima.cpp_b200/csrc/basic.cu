@@ -566,10 +566,39 @@ __global__ void head_gate_kernel(TO* __restrict__ o, long long o_stride, const f
     *p = from_f32<TO>(to_f32<TO>(*p) * s);
 }
 
+// The same, eight neighbouring values of one head a thread (head sizes that are multiples of 8, rows on 16-byte boundaries).
+template <typename TO>
+__global__ void head_gate_vec_kernel(TO* __restrict__ o, long long o_stride, const float* __restrict__ g, long long g_stride,
+                                     long long n8, int n_heads, int hd) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n8) return;
+    const int per = n_heads * hd / 8;
+    const long long t = i / per;
+    const int c = (int)(i % per) * 8;
+    const float s = 1.0f / (1.0f + expf(-g[t * g_stride + c / hd]));
+    float v[8];
+    load_vec<TO, 8>(o + t * o_stride + c, v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) v[k] *= s;
+    store_vec<TO, 8>(o + t * o_stride + c, v);
+}
+
 UB_API int ub_head_gate(void* o, int o_dtype, long long o_stride, const float* g, long long g_stride, int n_tokens,
                         int n_heads, int hd, cudaStream_t st) {
     const long long n = (long long)n_tokens * n_heads * hd;
     if (n <= 0) return 0;
+    const int esz = o_dtype == UB_F32 ? 4 : 2;
+    if (hd % 8 == 0 && ((uintptr_t)o & 15) == 0 && (o_stride * esz) % 16 == 0) {
+        const long long n8 = n / 8;
+        const unsigned grid8 = (unsigned)((n8 + 255) / 256);
+        cudaError_t e8;
+        if (o_dtype == UB_F32) e8 = ub_launch_dependent(head_gate_vec_kernel<float>, dim3(grid8), dim3(256), 0, st, (float*)o, o_stride, g, g_stride, n8, n_heads, hd);
+        else if (o_dtype == UB_BF16) e8 = ub_launch_dependent(head_gate_vec_kernel<__nv_bfloat16>, dim3(grid8), dim3(256), 0, st, (__nv_bfloat16*)o, o_stride, g, g_stride, n8, n_heads, hd);
+        else return UB_ERR_UNSUPPORTED;
+        return (int)e8;
+    }
     const unsigned grid = (unsigned)((n + 255) / 256);
     cudaError_t e;
     if (o_dtype == UB_F32) e = ub_launch_dependent(head_gate_kernel<float>, dim3(grid), dim3(256), 0, st, (float*)o, o_stride, g, g_stride, n, n_heads, hd);

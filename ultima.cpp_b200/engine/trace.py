@@ -64,7 +64,10 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time (each rounded up to 64)")
+                    help="most tokens live requests hold at any time, padding not counted (the cache adds a page of "
+                         "64 positions for every slot, since every live request may leave one partly filled)")
+    ap.add_argument("--max-seqs", type=int, default=0,
+                    help="requests alive at once (default: as many as --max-tokens allows, 16 to 256)")
     ap.add_argument("--max-step-tokens", type=int, default=4096)
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
@@ -75,7 +78,10 @@ def main(argv=None) -> int:
 
     print(f"[trace_run] loading {args.model} ({args.dtype})", file=sys.stderr, flush=True)
     from .engine import Engine
-    engine = Engine.from_dir(args.model, dtype=args.dtype, max_tokens=args.max_tokens,
+    from ..cache import PAGE
+    n_slots = args.max_seqs or max(16, min(256, args.max_tokens))
+    engine = Engine.from_dir(args.model, dtype=args.dtype, max_tokens=args.max_tokens + PAGE * n_slots, max_seqs=n_slots,
+                             max_context=-(-args.max_tokens // PAGE) * PAGE,
                              max_step_tokens=args.max_step_tokens, device=args.device, with_sampler=False)
     engine.warm_up()
     print("[trace_run] ready", file=sys.stderr, flush=True)
