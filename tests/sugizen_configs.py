@@ -52,4 +52,15 @@ WIDE = {"architecture": "Sugizen", "vocab": 384, "width": 128, "norm": {"eps": 1
     _layer("attention", _attention(6, 3, 48, 48, 0.15, {"base": 1000.0, "dims": 24}, 40), 128, 3.0),
 ]}
 
-CONFIGS = {"mixed": MIXED, "odd": ODD, "wide": WIDE}
+# only one kind of layer: a model without any keys and values, and one without any state
+DELTA_ONLY = {"architecture": "Sugizen", "vocab": 130, "width": 48, "norm": {"eps": 1e-5}, "layers": [
+    _layer("channel_delta", _delta(2, 2, 32, 32, 4, 8, 8), 64, 1.2),
+    _layer("channel_delta", _delta(6, 3, 16, 12, 3, 6, 3)),
+]}
+ATTENTION_ONLY = {"architecture": "Sugizen", "vocab": 210, "width": 72, "norm": {"eps": 2e-5}, "layers": [
+    _layer("attention", _attention(3, 1, 24, 40, 0.2, {"base": 777.0, "dims": 24}, 33), 100, 1.0),
+    _layer("attention", _attention(6, 1, 24, 40, 0.21, {"base": 777.0, "dims": 24}, 50, kv_from=0)),
+    _layer("attention", _attention(2, 2, 16, 16, 0.25), 40, 9.0),
+]}
+
+CONFIGS = {"mixed": MIXED, "odd": ODD, "wide": WIDE, "delta_only": DELTA_ONLY, "attention_only": ATTENTION_ONLY}
