@@ -39,10 +39,12 @@ __device__ __forceinline__ float proj_at(const float* __restrict__ p, const Delt
 }
 
 // One warp a (token, unit); units of a token: G query heads, G key heads, H value heads (which also
-// make the head's write strength and decay).
+// make the head's write strength and decay).  ``update_state`` (only when every sequence brings ONE token, so
+// that a channel's state has this lane as its only reader): the convolution's state moves on here, and
+// conv_state_update is not launched.
 __global__ void __launch_bounds__(128)
 delta_prepare_kernel(const float* __restrict__ p, DeltaShape s, const float* __restrict__ conv_w,
-                     const float* __restrict__ conv_state, const float* __restrict__ dpre,
+                     float* conv_state, int update_state, const float* __restrict__ dpre,
                      const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                      const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
                      const int* __restrict__ seq_slot, float* __restrict__ qn, float* __restrict__ kn,
@@ -59,7 +61,7 @@ delta_prepare_kernel(const float* __restrict__ p, DeltaShape s, const float* __r
     const int r = t - seq_start[seq];
     const int K = s.taps - 1;
     const int C = 2 * s.G * s.D + s.H * s.E;
-    const float* st = conv_state + (long long)seq_slot[seq] * K * C;
+    float* st = conv_state + (long long)seq_slot[seq] * K * C;
 
     auto conv_silu = [&](int c) -> float {
         float acc = 0.f;
@@ -67,6 +69,7 @@ delta_prepare_kernel(const float* __restrict__ p, DeltaShape s, const float* __r
             const float w = conv_w[(long long)c * s.taps + (s.taps - 1 - j)];
             const float x = (r - j >= 0) ? proj_at(p, s, t - j, c) : st[(long long)(K + r - j) * C + c];
             acc = fmaf(w, x, acc);
+            if (update_state && j < K) st[(long long)(K - 1 - j) * C + c] = x;     // r = 0: the input j back becomes j + 1 back
         }
         return acc * sigmoidf_(acc);
     };
@@ -342,8 +345,8 @@ static int read_shape(const int* shape, long long ldp, int n_parts, long long pa
 }
 
 UB_API int ub_delta_prepare(const float* p, long long ldp, int n_parts, long long part_stride, const int* shape,
-                            const float* conv_w, const float* conv_state, const float* dpre, const float* dt_bias,
-                            const float* a_log, const int* tok_seq,
+                            const float* conv_w, float* conv_state, int update_state, const float* dpre,
+                            const float* dt_bias, const float* a_log, const int* tok_seq,
                             const int* seq_start, const int* seq_slot, float* qn, float* kn, float* vc, float* beta,
                             float* dec, int n_tokens, float unit_eps, float q_scale, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
@@ -351,7 +354,7 @@ UB_API int ub_delta_prepare(const float* p, long long ldp, int n_parts, long lon
     if (int rc = read_shape(shape, ldp, n_parts, part_stride, s)) return rc;
     const long long warps = (long long)n_tokens * (2 * s.G + s.H);
     const unsigned grid = (unsigned)((warps + 3) / 4);
-    return (int)ub_launch_dependent(delta_prepare_kernel, dim3(grid), dim3(128), 0, st, p, s, conv_w, conv_state, dpre, dt_bias,
+    return (int)ub_launch_dependent(delta_prepare_kernel, dim3(grid), dim3(128), 0, st, p, s, conv_w, conv_state, update_state, dpre, dt_bias,
                                     a_log, tok_seq, seq_start, seq_slot, qn, kn, vc, beta, dec, n_tokens, unit_eps, q_scale);
 }
 

@@ -114,7 +114,7 @@ def _declare(lib, source: str) -> None:
         "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, L, P],
                            "ub_qkv_place": [P, I, L, I, L, I, I, I, P, I, L, P, P, P, P, I, P, P, P, P, I, P, I, I, I, I, I,
                                             I, I, I, F, I, P, P]},
-        "delta.cu": {"ub_delta_prepare": [P, L, I, L, P, P, P, P, P, P, P, P, P, P, P, P, P, P, I, F, F, P],
+        "delta.cu": {"ub_delta_prepare": [P, L, I, L, P, P, P, I, P, P, P, P, P, P, P, P, P, P, P, I, F, F, P],
                      "ub_conv_state_update": [P, L, I, L, P, P, P, I, I, I, P],
                      "ub_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
                      "ub_delta_finish": [P, P, P, P, I, I, I, I, F, P]},
@@ -375,16 +375,21 @@ def _parts_of(p):
     return p.shape[0], p.stride(0), 1, 0
 
 
-def delta_prepare(p, shape, conv_w, conv_state, decay_pre, dt_bias, a_log, batch, qn, kn, vc, beta, dec, unit_eps, q_scale):
+def delta_prepare(p, shape, conv_w, conv_state, decay_pre, dt_bias, a_log, batch, qn, kn, vc, beta, dec, unit_eps, q_scale,
+                  update_state=False):
     """p: the projections [q | k | v | write strength] in float32; decay_pre [T, heads * key size]: the decay's
-    sums before the bias.  Fills qn, kn (unit vectors), vc, beta and dec."""
+    sums before the bias.  Fills qn, kn (unit vectors), vc, beta and dec.  ``update_state`` (every sequence brings
+    one token): the convolution's state moves on in this kernel, and ``conv_state_update`` is not needed."""
     _need_cuda(p, conv_w, conv_state, decay_pre, qn, kn, vc, beta, dec)
     assert p.dtype == torch.float32
     T, ldp, n_parts, part_stride = _parts_of(p)
     for t in (conv_w, conv_state, decay_pre, dt_bias, a_log, qn, kn, vc, beta, dec):
         assert t.dtype == torch.float32 and t.is_contiguous()
+    if update_state:
+        assert batch.n_seqs == T, "the state moves on in this kernel only when every sequence brings one token"
     _check(_lib("delta.cu").ub_delta_prepare(
-        _ptr(p), ldp, n_parts, part_stride, shape, _ptr(conv_w), _ptr(conv_state), _ptr(decay_pre), _ptr(dt_bias),
+        _ptr(p), ldp, n_parts, part_stride, shape, _ptr(conv_w), _ptr(conv_state), 1 if update_state else 0,
+        _ptr(decay_pre), _ptr(dt_bias),
         _ptr(a_log), _ptr(batch.tok_seq), _ptr(batch.seq_start), _ptr(batch.seq_slot), _ptr(qn), _ptr(kn), _ptr(vc),
         _ptr(beta), _ptr(dec), T, float(unit_eps), float(q_scale), _stream()), "delta_prepare")
 

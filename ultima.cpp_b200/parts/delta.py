@@ -119,10 +119,13 @@ class GatedDelta(Mixer):
         dec = rt.arena.alloc((T, self.nh * self.hd), f32)
         o = rt.arena.alloc((T, self.v_width), f32)
         oa = rt.arena.alloc((T, self.v_width), rt.dtype)
-        rt.launches += 4
+        # one token a sequence: a channel's state has one reader, which then also moves it on
+        one_each = batch.max_new == 1 and batch.n_seqs == T
+        rt.launches += 3 if one_each else 4
         ops.delta_prepare(p, self.shape, self.conv_w, conv_state, decay_pre, self.dt_bias, self.a_log, batch,
-                          qn, kn, vc, beta, dec, self.unit_eps, self.hd ** -0.5)
-        ops.conv_state_update(p, conv_state, batch, self.channels, self.conv)
+                          qn, kn, vc, beta, dec, self.unit_eps, self.hd ** -0.5, update_state=one_each)
+        if not one_each:
+            ops.conv_state_update(p, conv_state, batch, self.channels, self.conv)
         ops.delta_scan(qn, kn, vc, beta, dec, o, S, batch, self.nh, self.nkv, self.hd, self.hdv)
         ops.delta_finish(o, gate_pre, self.o_norm, oa, self.nh, self.hdv, self.eps)
         rt.matmul(oa, self.wo, residual, ops.EPI_ADD)
