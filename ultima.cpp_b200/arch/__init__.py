@@ -11,6 +11,7 @@ import os
 from ..config.base import find_architecture
 from . import qwen3  # registers Qwen3ForCausalLM
 from . import sugizen  # registers Sugizen
+from . import tinuzen  # registers Tinuzen
 
 for _name in filter(None, (m.strip() for m in os.environ.get("ULTIMA_ARCH_MODULES", "").split(","))):
     importlib.import_module(_name)

@@ -10,10 +10,14 @@
 //
 // Beyond the reference: values may have a head size of their own (``hd_v``); ``block`` > 0 masks by
 // blocks of positions counted from the sequence's start (p sees j <= p with j / block == p / block);
-// ``gate`` (float32, one number a token and head) multiplies a head's output by its sigmoid.  The
-// placement kernel at the end prepares queries and fills the cache from projection rows whose q, k and
+// ``gate`` (float32, one number a token and head, or ``gate_wide`` one a token and output element)
+// multiplies the output by its sigmoid.  Further options, all off at zero: ``keep_first`` > 0 with a
+// window: the sequence's first keep_first positions stay visible behind the window; ``slopes`` (float32,
+// one a head): slope * (distance to the key) is taken off a score; ``sink``: the softmax's sum has one
+// more term exp(0) that brings no value; ``out_scale`` multiplies the output.  The
+// placement kernels at the end prepare queries and fill the cache from projection rows whose q, k and
 // v columns lie anywhere, for layers the fused preparation of basic.cu does not take (unequal head
-// sizes, no keys and values of their own).
+// sizes, no keys and values of their own, a norm over all heads at once, values that are the keys).
 #include "common.cuh"
 
 constexpr int CHUNK = 512;
@@ -23,7 +27,8 @@ __global__ void __launch_bounds__(128)
 attn_simple_kernel(const TQ* __restrict__ q, long long q_stride, const TC* __restrict__ kc,
                    const TC* __restrict__ vc, TQ* __restrict__ out, long long o_stride,
                    const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, PagedKV c, PagedKV cv,
-                   int nh, int window, int block, const float* __restrict__ gate, long long g_stride, float scale) {
+                   int nh, int window, int block, const float* __restrict__ gate, long long g_stride, float scale,
+                   int keep_first, const float* __restrict__ slopes, int sink, int gate_wide, float out_scale) {
     extern __shared__ float smem[];
     float* qs = smem;                    // [hd]
     float* sc = smem + c.head_dim;       // [CHUNK]
@@ -37,15 +42,21 @@ attn_simple_kernel(const TQ* __restrict__ q, long long q_stride, const TC* __res
     if (block > 0) lo = max(lo, pos - pos % block);
     for (int i = tid; i < hd; i += blockDim.x) qs[i] = to_f32<TQ>(q[(long long)t * q_stride + (long long)h * hd + i]);
     __syncthreads();
-    float m = -INFINITY, l = 0.f, acc0 = 0.f, acc1 = 0.f;
-    for (int c0 = lo; c0 <= pos; c0 += CHUNK) {
-        const int n = min(CHUNK, pos + 1 - c0);
+    // the sink is a key with score 0 and no value: the running maximum and sum start from it
+    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f, acc0 = 0.f, acc1 = 0.f;
+    // visible keys: the kept first positions that the window has left behind, then lo .. pos
+    const int n_kept = min(max(keep_first, 0), lo);
+    const int n_keys = n_kept + pos + 1 - lo;
+    const float slope = slopes ? slopes[h] : 0.f;
+    for (int c0 = 0; c0 < n_keys; c0 += CHUNK) {
+        const int n = min(CHUNK, n_keys - c0);
         float cmax = -INFINITY;
         for (int j = tid; j < n; j += blockDim.x) {
-            const TC* kr = kc + paged_offset(c, seq, c0 + j, kvh);
+            const int key = c0 + j < n_kept ? c0 + j : lo + (c0 + j - n_kept);
+            const TC* kr = kc + paged_offset(c, seq, key, kvh);
             float s = 0.f;
             for (int i = 0; i < hd; ++i) s = fmaf(qs[i], to_f32<TC>(kr[i]), s);
-            s *= scale;
+            s = s * scale - slope * (float)(pos - key);
             sc[j] = s;
             cmax = fmaxf(cmax, s);
         }
@@ -64,18 +75,20 @@ attn_simple_kernel(const TQ* __restrict__ q, long long q_stride, const TC* __res
         acc0 *= corr;
         acc1 *= corr;
         for (int j = 0; j < n; ++j) {
-            const TC* vr = vc + paged_offset(cv, seq, c0 + j, kvh);
+            const int key = c0 + j < n_kept ? c0 + j : lo + (c0 + j - n_kept);
+            const TC* vr = vc + paged_offset(cv, seq, key, kvh);
             const float p = sc[j];
             if (tid < hdv) acc0 = fmaf(p, to_f32<TC>(vr[tid]), acc0);
             if (tid + 128 < hdv) acc1 = fmaf(p, to_f32<TC>(vr[tid + 128]), acc1);
         }
         __syncthreads();
     }
-    float inv = 1.0f / l;
-    if (gate) inv *= 1.0f / (1.0f + expf(-gate[(long long)t * g_stride + h]));
+    float inv = out_scale / l;
+    if (gate && !gate_wide) inv *= 1.0f / (1.0f + expf(-gate[(long long)t * g_stride + h]));
     TQ* o = out + (long long)t * o_stride + (long long)h * hdv;
-    if (tid < hdv) o[tid] = from_f32<TQ>(acc0 * inv);
-    if (tid + 128 < hdv) o[tid + 128] = from_f32<TQ>(acc1 * inv);
+    const float* gw = gate && gate_wide ? gate + (long long)t * g_stride + (long long)h * hdv : nullptr;
+    if (tid < hdv) o[tid] = from_f32<TQ>(acc0 * inv * (gw ? 1.0f / (1.0f + expf(-gw[tid])) : 1.0f));
+    if (tid + 128 < hdv) o[tid + 128] = from_f32<TQ>(acc1 * inv * (gw ? 1.0f / (1.0f + expf(-gw[tid + 128])) : 1.0f));
 }
 
 // q: [T, *] with row stride q_stride (elements), heads side by side; out likewise.
@@ -83,16 +96,19 @@ UB_API int ub_attn_simple(const void* q, long long q_stride, int act_dtype, cons
                           const void* vcache, int cache_dtype, void* out, long long o_stride,
                           const int* tok_pos, const int* tok_seq, const int* table, int pages_per_seq,
                           int ring, int page, int n_tokens, int nh, int nkv, int hd, int window,
-                          float scale, int hd_v, int block, const float* gate, long long g_stride, cudaStream_t st) {
+                          float scale, int hd_v, int block, const float* gate, long long g_stride, int keep_first,
+                          const float* slopes, int sink, int gate_wide, float out_scale, cudaStream_t st) {
     if (n_tokens <= 0) return 0;
     if (hd_v <= 0) hd_v = hd;
     if (hd > 256 || hd <= 0 || hd_v > 256 || nh % nkv != 0 || ring % page != 0 || nh > 65535 || block < 0) return UB_ERR_ARG;
+    if (keep_first < 0 || (keep_first > 0 && block > 0)) return UB_ERR_ARG;
     PagedKV c{table, pages_per_seq, ring, page, nkv, hd};
     PagedKV cv{table, pages_per_seq, ring, page, nkv, hd_v};
     dim3 grid(n_tokens, nh);
     const size_t sm = (size_t)(hd + CHUNK) * sizeof(float);
 #define GO(TQ, TC) attn_simple_kernel<TQ, TC><<<grid, 128, sm, st>>>((const TQ*)q, q_stride, (const TC*)kcache, \
-        (const TC*)vcache, (TQ*)out, o_stride, tok_pos, tok_seq, c, cv, nh, window, block, gate, g_stride, scale)
+        (const TC*)vcache, (TQ*)out, o_stride, tok_pos, tok_seq, c, cv, nh, window, block, gate, g_stride, scale, \
+        keep_first, slopes, sink, gate_wide, out_scale)
     if (act_dtype == UB_F32 && cache_dtype == UB_F32) GO(float, float);
     else if (act_dtype == UB_BF16 && cache_dtype == UB_BF16) GO(__nv_bfloat16, __nv_bfloat16);
     else if (act_dtype == UB_F32 && cache_dtype == UB_BF16) GO(float, __nv_bfloat16);
@@ -204,6 +220,121 @@ UB_API int ub_qkv_place(const void* x, int x_dtype, long long ldx, int n_parts, 
     cudaError_t e;
 #define GO(TX, TQ, TC) e = ub_launch_dependent(qkv_place_kernel<TX, TQ, TC>, dim3(grid), dim3(128), 0, st, (const TX*)x, ldx, n_parts, \
         part_stride, q_off, k_off, v_off, (TQ*)q_out, ldq, qw, kw, cs, sn, rd, tok_pos, tok_seq, (TC*)kcache, (TC*)vcache, c, cv, n_tokens, nh, eps, g_off, gate_out)
+    if (x_dtype == UB_F32 && q_dtype == UB_F32 && cache_dtype == UB_F32) GO(float, float, float);
+    else if (x_dtype == UB_F32 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) GO(float, __nv_bfloat16, __nv_bfloat16);
+    else if (x_dtype == UB_BF16 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+    else return UB_ERR_UNSUPPORTED;
+#undef GO
+    return (int)e;
+}
+
+
+// ---------------------------------------------------------------------------------------
+// Placement by rows: the same task as above with one block a token, for layers whose norm runs over all
+// query heads (and all key heads) of a token at once (``norm_whole``: the weights then have one entry a
+// column of the projection, not one a column of a head), whose rotation pairs neighbouring columns
+// (``interleaved``: (2j, 2j + 1) instead of (j, j + rd/2)), or whose values are columns of the same row
+// taken as they are (v_off may equal k_off: the values are then the keys before norm and rotation).
+// gate_out (optional, float32 [T, g_width]) receives the g_width columns from g_off on, summed over parts.
+// The token's query and key columns are summed once into shared memory.
+// ---------------------------------------------------------------------------------------
+template <typename TX, typename TQ, typename TC>
+__global__ void __launch_bounds__(256)
+qkv_place_rows_kernel(const TX* __restrict__ x, long long ldx, int n_parts, long long part_stride, int q_off, int k_off, int v_off,
+                      TQ* __restrict__ q_out, long long ldq, const float* __restrict__ qw, const float* __restrict__ kw,
+                      int norm_whole, const float* __restrict__ cs, const float* __restrict__ sn, int rd, int interleaved,
+                      const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, TC* __restrict__ kc, TC* __restrict__ vc,
+                      PagedKV c, PagedKV cv, int nh, float eps, int g_off, int g_width, float* __restrict__ gate_out) {
+    extern __shared__ float row[];                  // [nh * hd] queries, then [nkv * hd] keys
+    __shared__ float red[33];
+    pdl_trigger();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, n_warps = blockDim.x >> 5;
+    const int hd = c.head_dim, nkv = k_off >= 0 ? c.n_kv_heads : 0;
+    const int qn = nh * hd, kn = nkv * hd;
+    const int pos = tok_pos[t], seq = tok_seq[t];
+    auto at = [&](int col) -> float {
+        float v = 0.f;
+        for (int p = 0; p < n_parts; ++p) v += to_f32<TX>(x[p * part_stride + t * ldx + col]);
+        return v;
+    };
+    float sq = 0.f, sk = 0.f;
+    for (int i = tid; i < qn + kn; i += blockDim.x) {
+        const float v = at(i < qn ? q_off + i : k_off + (i - qn));
+        row[i] = v;
+        if (i < qn) sq += v * v; else sk += v * v;
+    }
+    float inv_q = 1.f, inv_k = 1.f;
+    if (norm_whole) {
+        if (qw) inv_q = inv_rms(block_sum(sq, red), (float)qn, eps);
+        if (kw && kn) inv_k = inv_rms(block_sum(sk, red), (float)kn, eps);
+    }
+    __syncthreads();
+    const int half = rd >> 1;
+    for (int unit = warp; unit < nh + nkv; unit += n_warps) {
+        const bool is_q = unit < nh;
+        const int head = is_q ? unit : unit - nh;
+        float* my = row + (is_q ? 0 : qn) + head * hd;
+        const float* w = is_q ? qw : kw;
+        if (w) {
+            float inv = is_q ? inv_q : inv_k;
+            if (!norm_whole) {
+                float ss = 0.f;
+                for (int d = lane; d < hd; d += 32) ss += my[d] * my[d];
+                inv = inv_rms(warp_sum(ss), (float)hd, eps);
+            }
+            const float* wh = norm_whole ? w + head * hd : w;
+            for (int d = lane; d < hd; d += 32) my[d] *= inv * wh[d];
+            __syncwarp();
+        }
+        for (int d = lane; d < hd; d += 32) {
+            float o = my[d];
+            if (cs && d < rd) {
+                if (interleaved) {
+                    const int j = d >> 1;
+                    const float cj = cs[(long long)pos * half + j], sj = sn[(long long)pos * half + j];
+                    o = (d & 1) ? my[d] * cj + my[d - 1] * sj : my[d] * cj - my[d + 1] * sj;
+                } else {
+                    const int j = d < half ? d : d - half;
+                    const float cj = cs[(long long)pos * half + j], sj = sn[(long long)pos * half + j];
+                    o = d < half ? my[d] * cj - my[d + half] * sj : my[d] * cj + my[d - half] * sj;
+                }
+            }
+            if (is_q) q_out[t * ldq + (long long)head * hd + d] = from_f32<TQ>(o);
+            else kc[paged_offset(c, seq, pos, head) + d] = from_f32<TC>(o);
+        }
+    }
+    if (k_off >= 0) {
+        const int hdv = cv.head_dim;
+        for (int i = tid; i < nkv * hdv; i += blockDim.x) {
+            const int g = i / hdv, e = i % hdv;
+            vc[paged_offset(cv, seq, pos, g) + e] = from_f32<TC>(at(v_off + i));
+        }
+    }
+    if (gate_out)
+        for (int i = tid; i < g_width; i += blockDim.x) gate_out[t * g_width + i] = at(g_off + i);
+}
+
+UB_API int ub_qkv_place_rows(const void* x, int x_dtype, long long ldx, int n_parts, long long part_stride, int q_off, int k_off,
+                             int v_off, void* q_out, int q_dtype, long long ldq, const float* qw, const float* kw, int norm_whole,
+                             const float* cs, const float* sn, int rd, int interleaved, const int* tok_pos, const int* tok_seq,
+                             void* kcache, void* vcache, int cache_dtype, const int* table, int pages_per_seq, int ring, int page,
+                             int n_tokens, int nh, int nkv, int hd, int hd_v, float eps, int g_off, int g_width, float* gate_out,
+                             cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (hd <= 0 || hd_v <= 0 || nh <= 0 || nkv <= 0 || n_parts < 1 || (cs && (rd % 2 || rd < 2 || rd > hd)) ||
+        ring % page != 0) return UB_ERR_ARG;
+    const size_t smem = (size_t)(nh + (k_off >= 0 ? nkv : 0)) * hd * sizeof(float);
+    if (smem > 200 * 1024) return UB_ERR_ARG;
+    PagedKV c{table, pages_per_seq, ring, page, nkv, hd};
+    PagedKV cv{table, pages_per_seq, ring, page, nkv, hd_v};
+    cudaError_t e;
+#define GO(TX, TQ, TC) do { \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(qkv_place_rows_kernel<TX, TQ, TC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        e = ub_launch_dependent(qkv_place_rows_kernel<TX, TQ, TC>, dim3(n_tokens), dim3(256), smem, st, (const TX*)x, ldx, n_parts, \
+            part_stride, q_off, k_off, v_off, (TQ*)q_out, ldq, qw, kw, norm_whole, cs, sn, rd, interleaved, tok_pos, tok_seq, \
+            (TC*)kcache, (TC*)vcache, c, cv, nh, eps, g_off, g_width, gate_out); } while (0)
     if (x_dtype == UB_F32 && q_dtype == UB_F32 && cache_dtype == UB_F32) GO(float, float, float);
     else if (x_dtype == UB_F32 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) GO(float, __nv_bfloat16, __nv_bfloat16);
     else if (x_dtype == UB_BF16 && q_dtype == UB_BF16 && cache_dtype == UB_BF16) GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);

@@ -530,7 +530,8 @@ __global__ void glu_clamped_kernel(const TI* __restrict__ gu, TO* __restrict__ o
     const int f = (int)(i % F);
     const float g = fminf(to_f32<TI>(gu[t * 2 * F + f]), limit);
     const float u = fminf(fmaxf(to_f32<TI>(gu[t * 2 * F + F + f]), -limit), limit);
-    out[i] = from_f32<TO>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+    // an infinite alpha is the sigmoid's hard limit: the gate passes g where it is positive (a rectifier)
+    out[i] = from_f32<TO>((isinf(alpha) ? fmaxf(g, 0.f) : g / (1.0f + expf(-alpha * g))) * (u + shift));
 }
 
 UB_API int ub_glu_clamped(const void* gu, int in_dtype, void* out, int out_dtype, int n_tokens, int F,
@@ -760,4 +761,166 @@ UB_API int ub_fill_normal(void* out, int dtype, long long n, unsigned long long 
     else return UB_ERR_UNSUPPORTED;
     UB_LAUNCH_CHECK();
     return 0;
+}
+
+// ---------------------------------------------------------------------------------------
+// Embedding with a second, hashed table: x[t, :] = scale * table[id_t, :] + pairs[row_t, :], where
+// row_t = (prev_t * mul_prev + id_t * mul_cur) mod buckets and prev_t is the token before t in its
+// sequence; a sequence's first token takes row ``buckets`` (the table has buckets + 1 rows).  The token
+// before a step's first one is per-sequence state: ``last`` [slots] holds it plus one (zero: none yet).
+// The block of a sequence's first row of the step reads it and then stores the step's last token there.
+// ---------------------------------------------------------------------------------------
+template <typename TT>
+__global__ void embed_pairs_kernel(const TT* __restrict__ table, const TT* __restrict__ pairs, const int* __restrict__ ids,
+                                   const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                                   const int* __restrict__ seq_slot, int* last, float* __restrict__ x, int width, int vocab,
+                                   float scale, int buckets, long long mul_prev, long long mul_cur, int* status) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    const int s = tok_seq[t];
+    const int first = seq_start[s];
+    int prev;
+    if (t > first) prev = ids[t - 1];
+    else prev = last[seq_slot[s]] - 1;
+    const bool ok = id >= 0 && id < vocab && prev < vocab;
+    if (!ok && threadIdx.x == 0) atomicExch(status, 1);
+    long long row = buckets;
+    if (prev >= 0 && ok) {
+        row = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+        if (row < 0) row += buckets;
+    }
+    const TT* e = table + (long long)(ok ? id : 0) * width;
+    const TT* b = pairs + row * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        x[(long long)t * width + i] = ok ? fmaf(to_f32<TT>(e[i]), scale, to_f32<TT>(b[i])) : 0.f;
+    if (t == first) {
+        __syncthreads();                                   // every thread of this block has read ``last``
+        if (threadIdx.x == 0) last[seq_slot[s]] = ids[seq_start[s + 1] - 1] + 1;
+    }
+}
+
+UB_API int ub_embed_pairs(const void* table, const void* pairs, int table_dtype, const int* ids, const int* tok_seq,
+                          const int* seq_start, const int* seq_slot, int* last, float* x, int n_tokens, int width,
+                          int vocab, float scale, int buckets, long long mul_prev, long long mul_cur, int* status,
+                          cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    if (buckets < 1) return UB_ERR_ARG;
+    const int threads = width >= 1024 ? 256 : 128;
+    cudaError_t e;
+    if (table_dtype == UB_F32)
+        e = ub_launch_dependent(embed_pairs_kernel<float>, dim3(n_tokens), dim3(threads), 0, st, (const float*)table, (const float*)pairs,
+                                ids, tok_seq, seq_start, seq_slot, last, x, width, vocab, scale, buckets, mul_prev, mul_cur, status);
+    else if (table_dtype == UB_BF16)
+        e = ub_launch_dependent(embed_pairs_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, st, (const __nv_bfloat16*)table,
+                                (const __nv_bfloat16*)pairs, ids, tok_seq, seq_start, seq_slot, last, x, width, vocab, scale, buckets,
+                                mul_prev, mul_cur, status);
+    else return UB_ERR_UNSUPPORTED;
+    return (int)e;
+}
+
+// ---------------------------------------------------------------------------------------
+// A sublayer's result joins the stream through a gate: x += sigmoid(g + b) * y, all float32; g is the
+// gate's sums ([T, width], or the sum of ``n_parts`` partial results ``part_stride`` apart), b its bias
+// (optional).  ``clear_y``: y, which sublayers add their output into, is zeroed behind the read.
+// ---------------------------------------------------------------------------------------
+__global__ void gated_add_kernel(const float* __restrict__ g, int n_parts, long long part_stride, const float* __restrict__ b,
+                                 float* __restrict__ y, float* __restrict__ x, long long n, int width, int clear_y) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    const int c = (int)(i % width);
+    float4 s = *reinterpret_cast<const float4*>(g + i);
+    for (int p = 1; p < n_parts; ++p) {
+        const float4 q = *reinterpret_cast<const float4*>(g + p * part_stride + i);
+        s.x += q.x; s.y += q.y; s.z += q.z; s.w += q.w;
+    }
+    if (b) { s.x += b[c]; s.y += b[c + 1]; s.z += b[c + 2]; s.w += b[c + 3]; }
+    const float4 yv = *reinterpret_cast<const float4*>(y + i);
+    float4 xv = *reinterpret_cast<const float4*>(x + i);
+    xv.x = fmaf(yv.x, 1.0f / (1.0f + expf(-s.x)), xv.x);
+    xv.y = fmaf(yv.y, 1.0f / (1.0f + expf(-s.y)), xv.y);
+    xv.z = fmaf(yv.z, 1.0f / (1.0f + expf(-s.z)), xv.z);
+    xv.w = fmaf(yv.w, 1.0f / (1.0f + expf(-s.w)), xv.w);
+    *reinterpret_cast<float4*>(x + i) = xv;
+    if (clear_y) *reinterpret_cast<float4*>(y + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+}
+
+__global__ void gated_add_scalar_kernel(const float* __restrict__ g, int n_parts, long long part_stride, const float* __restrict__ b,
+                                        float* __restrict__ y, float* __restrict__ x, long long n, int width, int clear_y) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float s = 0.f;
+    for (int p = 0; p < n_parts; ++p) s += g[p * part_stride + i];
+    if (b) s += b[i % width];
+    x[i] = fmaf(y[i], 1.0f / (1.0f + expf(-s)), x[i]);
+    if (clear_y) y[i] = 0.f;
+}
+
+UB_API int ub_gated_add(const float* g, int n_parts, long long part_stride, const float* b, float* y, float* x, int n_rows,
+                        int width, int clear_y, cudaStream_t st) {
+    const long long n = (long long)n_rows * width;
+    if (n <= 0) return 0;
+    if (n_parts < 1) return UB_ERR_ARG;
+    cudaError_t e;
+    if (width % 4 == 0 && part_stride % 4 == 0 && (((uintptr_t)g | (uintptr_t)y | (uintptr_t)x) & 15) == 0)
+        e = ub_launch_dependent(gated_add_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, g, n_parts, part_stride, b,
+                                y, x, n, width, clear_y);
+    else
+        e = ub_launch_dependent(gated_add_scalar_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, g, n_parts, part_stride,
+                                b, y, x, n, width, clear_y);
+    return (int)e;
+}
+
+// ---------------------------------------------------------------------------------------
+// x[r, :] += a[r, :] + v[:]   (a optional: another stream of the same shape; v optional: one row for all)
+// ---------------------------------------------------------------------------------------
+__global__ void add_rows_kernel(float* __restrict__ x, const float* __restrict__ a, const float* __restrict__ v, long long n,
+                                int width) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float s = x[i];
+    if (a) s += a[i];
+    if (v) s += v[i % width];
+    x[i] = s;
+}
+
+UB_API int ub_add_rows(float* x, const float* a, const float* v, int n_rows, int width, cudaStream_t st) {
+    const long long n = (long long)n_rows * width;
+    if (n <= 0) return 0;
+    return (int)ub_launch_dependent(add_rows_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, x, a, v, n, width);
+}
+
+// ---------------------------------------------------------------------------------------
+// One gate an element: o[t, c] *= scale * sigmoid(g[t, c]), g float32 with a row stride of its own.
+// ---------------------------------------------------------------------------------------
+template <typename TO>
+__global__ void elem_gate_kernel(TO* __restrict__ o, long long o_stride, const float* __restrict__ g, long long g_stride,
+                                 long long n, int cols, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const long long t = i / cols;
+    const int c = (int)(i % cols);
+    TO* p = o + t * o_stride + c;
+    *p = from_f32<TO>(to_f32<TO>(*p) * scale / (1.0f + expf(-g[t * g_stride + c])));
+}
+
+UB_API int ub_elem_gate(void* o, int o_dtype, long long o_stride, const float* g, long long g_stride, int n_tokens, int cols,
+                        float scale, cudaStream_t st) {
+    const long long n = (long long)n_tokens * cols;
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned)((n + 255) / 256);
+    cudaError_t e;
+    if (o_dtype == UB_F32) e = ub_launch_dependent(elem_gate_kernel<float>, dim3(grid), dim3(256), 0, st, (float*)o, o_stride, g, g_stride, n, cols, scale);
+    else if (o_dtype == UB_BF16) e = ub_launch_dependent(elem_gate_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, (__nv_bfloat16*)o, o_stride, g, g_stride, n, cols, scale);
+    else return UB_ERR_UNSUPPORTED;
+    return (int)e;
 }

@@ -47,13 +47,15 @@ struct GemmParams {
     int share_tail;       // persistent EPI_ADD: the tiles of the last, part-empty round are shared out by k blocks
     int* error;           // raised on a timeout
     // the gate product's constants: out = g' / (1 + exp(-alpha g')) * (u' + shift) with g' = min(g, limit) and
-    // u' = clamp(u, -limit, limit); +inf, 1 and 0 give silu(g) * u with the same bits as without them
+    // u' = clamp(u, -limit, limit); +inf, 1 and 0 give silu(g) * u with the same bits as without them; alpha = +inf
+    // is the hard limit max(g', 0) * (u' + shift)
     float act_limit, act_alpha, act_shift;
 };
 
 __device__ __forceinline__ float gate_product(const GemmParams& p, float g, float u) {
     g = fminf(g, p.act_limit);
     u = fminf(fmaxf(u, -p.act_limit), p.act_limit);
+    if (isinf(p.act_alpha)) return fmaxf(g, 0.f) * (u + p.act_shift);      // the sigmoid's hard limit: a rectifier on the gate
     return g / (1.0f + __expf(-p.act_alpha * g)) * (u + p.act_shift);
 }
 

@@ -1,0 +1,260 @@
+// A selective state-space mixer with a scalar decay a head (the "state-space duality" form): for every
+// head a matrix S [N, P] (N state channels, P value channels) in float32, zero at a sequence's start, plus
+// the last inputs of a short causal convolution.  For one token of one head, with a step size dt > 0,
+// an input row B [N] and an output row C [N] (shared by the heads of a group) and the value x [P]:
+//     S <- exp(-exp(A_log) dt) S + dt B x^T;      y = S^T C + D x
+//
+// A projection row is laid out [z | x | B | C | dt]: the output gate, then the convolution's channels
+// (x, B, C), then one step size a head.  Four kernels, for prompts and single tokens alike (a step's
+// tokens of one sequence are rows seq_start[s] .. seq_start[s + 1] of the packed batch; state rows are
+// slot numbers):
+//   ssm_prepare            convolution + bias + SiLU of x, B, C; dt = softplus(. + dt_bias); the decay
+//   ssm_conv_state_update  the convolution's last inputs, carried to the next step
+//   ssm_scan               the recurrence
+//   ssm_finish             y silu(z), RMS norm in equal parts of the row, weight, output scale
+// Everything is float32; the projection comes in as float32 sums of the product (for few tokens as the
+// partial sums of K slices, which the kernels add up as they read).  Every column of S evolves on its
+// own and tokens are taken in order, so no sum depends on the batch or on how a prompt was cut.
+#include "common.cuh"
+
+constexpr int SSM_MAX_TAPS = 16;
+
+struct SsmShape {
+    int H, P, N, G;          // heads, value size, state size, groups of heads that share B and C
+    int taps;                // convolution length (the last tap is the current token's)
+    int z_off, x_off, b_off, c_off, dt_off;   // columns of a projection row; x, B, C follow one another
+    long long ldp;           // row stride of the projection
+    int n_parts;             // the projection row is the sum of this many partial results ...
+    long long part_stride;   // ... this many elements apart
+};
+
+__device__ __forceinline__ float ssm_proj(const float* __restrict__ p, const SsmShape& s, long long t, int c) {
+    float v = 0.f;
+    for (int i = 0; i < s.n_parts; ++i) v += p[i * s.part_stride + t * s.ldp + c];
+    return v;
+}
+__device__ __forceinline__ float ssm_softplus(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// One thread a (token, channel): the convolution's channels first, then one (dt, decay) a head.
+// ``update_state`` (only when every sequence brings ONE token, so that a channel's state has this thread
+// as its only reader): the convolution's state moves on here.
+__global__ void __launch_bounds__(256)
+ssm_prepare_kernel(const float* __restrict__ p, SsmShape s, const float* __restrict__ conv_w, const float* __restrict__ conv_b,
+                   float* conv_state, int update_state, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                   const int* __restrict__ tok_seq, const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                   float* __restrict__ xbc, float* __restrict__ dtv, float* __restrict__ dec, int n_tokens) {
+    pdl_trigger();
+    pdl_wait();
+    const int C = s.H * s.P + 2 * s.G * s.N;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_tokens * (C + s.H)) return;
+    const int t = (int)(i / (C + s.H)), c = (int)(i % (C + s.H));
+    if (c >= C) {
+        const int h = c - C;
+        const float dt = ssm_softplus(ssm_proj(p, s, t, s.dt_off + h) + dt_bias[h]);
+        dtv[(long long)t * s.H + h] = dt;
+        dec[(long long)t * s.H + h] = expf(-expf(a_log[h]) * dt);
+        return;
+    }
+    const int seq = tok_seq[t];
+    const int r = t - seq_start[seq];
+    const int K = s.taps - 1;
+    float* st = conv_state + (long long)seq_slot[seq] * K * C;
+    float acc = conv_b ? conv_b[c] : 0.f;
+    for (int j = K; j >= 0; --j) {                     // oldest input first
+        const float w = conv_w[(long long)c * s.taps + (K - j)];
+        const float x = (r - j >= 0) ? ssm_proj(p, s, t - j, s.x_off + c) : st[(long long)(K + r - j) * C + c];
+        acc = fmaf(w, x, acc);
+        if (update_state && j < K) st[(long long)(K - 1 - j) * C + c] = x;     // r = 0: the input j back becomes j + 1 back
+    }
+    xbc[(long long)t * C + c] = acc / (1.0f + expf(-acc));
+}
+
+// One thread a (sequence, channel): the last taps - 1 inputs of what the state held followed by the step's.
+__global__ void ssm_conv_state_update_kernel(const float* __restrict__ p, SsmShape s, float* __restrict__ conv_state,
+                                             const int* __restrict__ seq_start, const int* __restrict__ seq_slot,
+                                             int n_seqs) {
+    pdl_trigger();
+    pdl_wait();
+    const int C = s.H * s.P + 2 * s.G * s.N;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)n_seqs * C) return;
+    const int b = (int)(i / C), c = (int)(i % C);
+    const int K = s.taps - 1;
+    const int first = seq_start[b], n = seq_start[b + 1] - first;
+    float* st = conv_state + (long long)seq_slot[b] * K * C;
+    float tmp[SSM_MAX_TAPS];
+    for (int k = 0; k < K; ++k) {
+        const int rel = n - K + k;
+        tmp[k] = rel >= 0 ? ssm_proj(p, s, first + rel, s.x_off + c) : st[(long long)(K + rel) * C + c];
+    }
+    for (int k = 0; k < K; ++k) st[(long long)k * C + c] = tmp[k];
+}
+
+// The recurrence.  A block of 128 threads takes 16 value channels of one head of one sequence; eight lanes
+// hold one column of S, lane l the state channels l, l + 8, ...  Tokens come through shared memory a few
+// at a time (two buffers: the next tokens are fetched while these are worked on).  The state's update
+// does not wait for the read-out: a token costs two operations a state element and three exchanges.
+template <int R>
+__global__ void __launch_bounds__(128)
+ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, const float* __restrict__ dec,
+                const float* __restrict__ Dw, float* __restrict__ y, float* __restrict__ S,
+                const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int H, int P, int N, int G) {
+    constexpr int LANES = 8, COLS = 16, TT = 8, NP = LANES * R;
+    __shared__ float sB[2][TT][NP], sC[2][TT][NP];
+    __shared__ float sx[2][TT][COLS], sdt[2][TT], sa[2][TT];
+    pdl_trigger();
+    pdl_wait();
+    const int tid = threadIdx.x, col = tid / LANES, l = tid % LANES;
+    const int h = blockIdx.y, b = blockIdx.z, g = h / (H / G);
+    const int j = blockIdx.x * COLS + col;
+    const int t0 = seq_start[b], t1 = seq_start[b + 1];
+    if (t0 >= t1) return;
+    const int C = H * P + 2 * G * N;
+    float* Sh = S + ((long long)seq_slot[b] * H + h) * N * P;
+    float s[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int n = i * LANES + l;
+        s[i] = (n < N && j < P) ? Sh[(long long)n * P + j] : 0.f;
+    }
+    const float dh = Dw[h];
+    auto fetch = [&](int base, int buf) {
+        const int cnt = min(TT, t1 - base);
+        for (int idx = tid; idx < cnt * NP; idx += blockDim.x) {
+            const int tt = idx / NP, n = idx % NP;
+            const float* rowp = xbc + (long long)(base + tt) * C + H * P + g * N;
+            sB[buf][tt][n] = n < N ? rowp[n] : 0.f;
+            sC[buf][tt][n] = n < N ? rowp[G * N + n] : 0.f;
+        }
+        for (int idx = tid; idx < cnt * COLS; idx += blockDim.x) {
+            const int tt = idx / COLS, cc = idx % COLS;
+            const int jj = blockIdx.x * COLS + cc;
+            sx[buf][tt][cc] = jj < P ? xbc[(long long)(base + tt) * C + h * P + jj] : 0.f;
+        }
+        if (tid < cnt) {
+            sdt[buf][tid] = dtv[(long long)(base + tid) * H + h];
+            sa[buf][tid] = dec[(long long)(base + tid) * H + h];
+        }
+    };
+    fetch(t0, 0);
+    __syncthreads();
+    int buf = 0;
+    for (int base = t0; base < t1; base += TT, buf ^= 1) {
+        const int cnt = min(TT, t1 - base);
+        if (base + TT < t1) fetch(base + TT, buf ^ 1);     // (its readers passed the barrier at the end of the last round)
+        for (int tt = 0; tt < cnt; ++tt) {
+            const float a = sa[buf][tt];
+            const float xv = sx[buf][tt][col];
+            const float u = sdt[buf][tt] * xv;
+            float part = 0.f;
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                s[i] = fmaf(a, s[i], sB[buf][tt][i * LANES + l] * u);
+                part = fmaf(s[i], sC[buf][tt][i * LANES + l], part);
+            }
+            part += __shfl_xor_sync(0xffffffffu, part, 1);
+            part += __shfl_xor_sync(0xffffffffu, part, 2);
+            part += __shfl_xor_sync(0xffffffffu, part, 4);
+            if (l == 0 && j < P) y[((long long)(base + tt) * H + h) * P + j] = fmaf(dh, xv, part);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int n = i * LANES + l;
+        if (n < N && j < P) Sh[(long long)n * P + j] = s[i];
+    }
+}
+
+// One warp a (token, part of the row): v = y silu(z); v / rms(v) * w * scale.
+template <typename TO>
+__global__ void __launch_bounds__(128)
+ssm_finish_kernel(const float* __restrict__ y, const float* __restrict__ p, SsmShape s, const float* __restrict__ w,
+                  TO* __restrict__ out, int n_tokens, int n_groups, float eps, float scale) {
+    pdl_trigger();
+    pdl_wait();
+    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (wid >= (long long)n_tokens * n_groups) return;
+    const long long t = wid / n_groups;
+    const int grp = (int)(wid % n_groups);
+    const int inner = s.H * s.P, per = inner / n_groups;
+    const int c0 = grp * per;
+    auto gated = [&](int c) -> float {
+        const float z = ssm_proj(p, s, t, s.z_off + c);
+        return y[t * inner + c] * z / (1.0f + expf(-z));
+    };
+    float ss = 0.f;
+    for (int e = lane; e < per; e += 32) { const float v = gated(c0 + e); ss += v * v; }
+    ss = warp_sum(ss);
+    const float inv = inv_rms(ss, (float)per, eps) * scale;
+    for (int e = lane; e < per; e += 32) out[t * inner + c0 + e] = from_f32<TO>(gated(c0 + e) * inv * w[c0 + e]);
+}
+
+// ---------------------------------------------------------------------------------------
+// shape: [H, P, N, G, taps, z_off, x_off, b_off, c_off, dt_off] (10 ints)
+static int read_shape(const int* shape, long long ldp, int n_parts, long long part_stride, SsmShape& s) {
+    s.H = shape[0]; s.P = shape[1]; s.N = shape[2]; s.G = shape[3]; s.taps = shape[4];
+    s.z_off = shape[5]; s.x_off = shape[6]; s.b_off = shape[7]; s.c_off = shape[8]; s.dt_off = shape[9];
+    s.ldp = ldp; s.n_parts = n_parts; s.part_stride = part_stride;
+    if (s.H <= 0 || s.G <= 0 || s.H % s.G || s.P <= 0 || s.N <= 0 || s.N > 256 || s.taps < 1 || s.taps > SSM_MAX_TAPS ||
+        s.H > 65535 || n_parts < 1) return UB_ERR_ARG;
+    // the convolution's channels are consecutive columns: x, then B, then C
+    if (s.b_off != s.x_off + s.H * s.P || s.c_off != s.b_off + s.G * s.N) return UB_ERR_ARG;
+    return 0;
+}
+
+UB_API int ub_ssm_prepare(const float* p, long long ldp, int n_parts, long long part_stride, const int* shape,
+                          const float* conv_w, const float* conv_b, float* conv_state, int update_state, const float* dt_bias,
+                          const float* a_log, const int* tok_seq, const int* seq_start, const int* seq_slot, float* xbc,
+                          float* dtv, float* dec, int n_tokens, cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    SsmShape s;
+    if (int rc = read_shape(shape, ldp, n_parts, part_stride, s)) return rc;
+    const long long n = (long long)n_tokens * (s.H * s.P + 2 * s.G * s.N + s.H);
+    return (int)ub_launch_dependent(ssm_prepare_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, p, s, conv_w, conv_b,
+                                    conv_state, update_state, dt_bias, a_log, tok_seq, seq_start, seq_slot, xbc, dtv, dec, n_tokens);
+}
+
+UB_API int ub_ssm_conv_state_update(const float* p, long long ldp, int n_parts, long long part_stride, const int* shape,
+                                    float* conv_state, const int* seq_start, const int* seq_slot, int n_seqs, cudaStream_t st) {
+    if (n_seqs <= 0) return 0;
+    SsmShape s;
+    if (int rc = read_shape(shape, ldp, n_parts, part_stride, s)) return rc;
+    if (s.taps <= 1) return 0;
+    const long long n = (long long)n_seqs * (s.H * s.P + 2 * s.G * s.N);
+    return (int)ub_launch_dependent(ssm_conv_state_update_kernel, dim3((unsigned)((n + 127) / 128)), dim3(128), 0, st, p, s,
+                                    conv_state, seq_start, seq_slot, n_seqs);
+}
+
+UB_API int ub_ssm_scan(const float* xbc, const float* dtv, const float* dec, const float* Dw, float* y, float* S,
+                       const int* seq_start, const int* seq_slot, int n_seqs, int H, int P, int N, int G, cudaStream_t st) {
+    if (n_seqs <= 0) return 0;
+    if (H <= 0 || G <= 0 || H % G || P <= 0 || N <= 0 || N > 256 || H > 65535 || n_seqs > 65535) return UB_ERR_ARG;
+    const dim3 grid((P + 15) / 16, H, n_seqs), block(128);
+    const int per = (N + 7) / 8;
+    cudaError_t e;
+#define GO(RR) e = ub_launch_dependent(ssm_scan_kernel<RR>, grid, block, 0, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G)
+    if (per <= 2) GO(2); else if (per <= 4) GO(4); else if (per <= 8) GO(8); else if (per <= 16) GO(16); else GO(32);
+#undef GO
+    return (int)e;
+}
+
+UB_API int ub_ssm_finish(const float* y, const float* p, long long ldp, int n_parts, long long part_stride, const int* shape,
+                         const float* w, void* out, int out_dtype, int n_tokens, int n_groups, float eps, float scale,
+                         cudaStream_t st) {
+    if (n_tokens <= 0) return 0;
+    SsmShape s;
+    if (int rc = read_shape(shape, ldp, n_parts, part_stride, s)) return rc;
+    if (n_groups < 1 || (s.H * s.P) % n_groups) return UB_ERR_ARG;
+    const long long warps = (long long)n_tokens * n_groups;
+    const unsigned grid = (unsigned)((warps + 3) / 4);
+    cudaError_t e;
+    if (out_dtype == UB_F32)
+        e = ub_launch_dependent(ssm_finish_kernel<float>, dim3(grid), dim3(128), 0, st, y, p, s, w, (float*)out, n_tokens, n_groups, eps, scale);
+    else if (out_dtype == UB_BF16)
+        e = ub_launch_dependent(ssm_finish_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, st, y, p, s, w, (__nv_bfloat16*)out, n_tokens, n_groups, eps, scale);
+    else return UB_ERR_UNSUPPORTED;
+    return (int)e;
+}

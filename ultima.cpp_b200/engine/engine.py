@@ -82,7 +82,7 @@ class Engine:
         # decode steps (one token a sequence, every logit wanted) are captured as CUDA graphs,
         # one for each (number of sequences, slices of the key range); parts must allow it
         from .model import TRACE as _tracing
-        self.use_graphs = bool(use_graphs) and not _tracing and all(L.graph_safe for L in self.model.layers)
+        self.use_graphs = bool(use_graphs) and not _tracing and self.model.graph_safe
         self._graphs: dict = {}
 
     # ---- construction ------------------------------------------------------------------

@@ -58,6 +58,7 @@ class Model:
             arrangement = build_part("arrangement", L.arrangement)
             parts = {role: bound(family, L.part(role), L.name_of(role)) for role, family in L.roles().items()}
             self.layers.append(BuiltLayer(arrangement, parts))
+        self.entries = [bound("entry", ps, prefix) for ps, prefix in spec.entries]
         self.final_norm = bound("norm", spec.final_norm, spec.final_norm_name)
         self.head = build_part("head", spec.head)
         if spec.head.get("tied"):
@@ -68,17 +69,32 @@ class Model:
         for r in spec.runs:
             if not (0 <= r.layer < len(self.layers)):
                 raise ValueError(f"run list names layer {r.layer}; the model has {len(self.layers)}")
+            if r.entry is not None and not (0 <= r.entry < len(self.entries)):
+                raise ValueError(f"run list names entry {r.entry}; the model has {len(self.entries)}")
+        self._keeps_embedding = any(self.entries[r.entry].needs_embedding_output for r in spec.runs if r.entry is not None)
+        # an embedding that keeps per-sequence state gets a place in the cache behind the runs'
+        need = getattr(self.embedding, "cache_need", None)
+        self._embedding_need = need() if need is not None else None
         self._stack = None            # see _stack_plan
+        self.tap = None               # a callable (run index, residual stream): called behind every run (for comparisons)
 
     def all_parts(self) -> list:
-        return [self.embedding, self.final_norm, self.head] + [p for L in self.layers for p in L.parts.values()]
+        return [self.embedding, self.final_norm, self.head] + self.entries + [p for L in self.layers for p in L.parts.values()]
+
+    @property
+    def graph_safe(self) -> bool:
+        return all(L.graph_safe for L in self.layers) and all(e.graph_safe for e in self.entries)
 
     def cache_needs(self):
-        """For each run of the run list, what its layer asks of the cache."""
-        return [self.layers[r.layer].cache_need() for r in self.spec.runs]
+        """For each run of the run list, what its layer asks of the cache; behind them, what the embedding
+        asks (an embedding with state of its own: the entry with index ``len(runs)``)."""
+        needs = [self.layers[r.layer].cache_need() for r in self.spec.runs]
+        if self._embedding_need is not None:
+            needs.append(self._embedding_need)
+        return needs
 
     def cache_sources(self):
-        return [r.cache_from for r in self.spec.runs]
+        return [r.cache_from for r in self.spec.runs] + ([None] if self._embedding_need is not None else [])
 
     def _stack_plan(self, cache):
         """The plan that runs all layers of a decode step as one resident kernel, if this model's layers
@@ -95,18 +111,29 @@ class Model:
         rt = self.rt
         rt.arena.reset(0)
         rt.pass_id += 1
-        x = self.embedding.forward(batch.tok_ids, rt)
+        if self._embedding_need is not None:
+            x = self.embedding.forward_step(batch, cache.run_cache(len(self.spec.runs), batch.tables), rt)
+        else:
+            x = self.embedding.forward(batch.tok_ids, rt)
         if TRACE:
             _trace("embd", 0, x)
+        x0 = None
+        if self._keeps_embedding:
+            x0 = rt.arena.alloc(tuple(x.shape), x.dtype)
+            x0.copy_(x)
         plan = self._stack_plan(cache) if (batch.max_new == 1 and batch.n_tokens <= 64) else None
         if plan is not None:
             plan.run(x, batch)                    # one token a sequence: the whole stack in one kernel
         else:
             for i, r in enumerate(self.spec.runs):
                 layer = self.layers[r.layer]
+                if r.entry is not None:
+                    self.entries[r.entry].forward(x, x0, rt)
                 layer.arrangement.run(layer, x, batch, cache.run_cache(i, batch.tables), rt)
                 if TRACE:
                     _trace("l_out", i, x)
+                if self.tap is not None:
+                    self.tap(i, x)
         if batch.want_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=rt.device)
         h = self.final_norm.forward(x, rt, rows=batch.want_rows)

@@ -109,15 +109,25 @@ def _declare(lib, source: str) -> None:
             "ub_convert": [P, I, P, I, L, P],
             "ub_add_into": [P, P, I, L, P],
             "ub_fill_normal": [P, I, L, U, F, F, P],
+            "ub_embed_pairs": [P, P, I, P, P, P, P, P, P, I, I, I, F, I, L, L, P, P],
+            "ub_gated_add": [P, I, L, P, P, P, I, I, I, P],
+            "ub_add_rows": [P, P, P, I, I, P],
+            "ub_elem_gate": [P, I, L, P, L, I, I, F, P],
         },
         "gemm_simt.cu": {"ub_gemm_simt": [P, I, P, P, I, P, I, I, I, I, L, L, L, I, P]},
-        "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, L, P],
+        "attn_simple.cu": {"ub_attn_simple": [P, L, I, P, P, I, P, L, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, L, I, P, I, I, F, P],
+                           "ub_qkv_place_rows": [P, I, L, I, L, I, I, I, P, I, L, P, P, I, P, P, I, I, P, P, P, P, I, P, I, I, I, I, I,
+                                                 I, I, I, F, I, I, P, P],
                            "ub_qkv_place": [P, I, L, I, L, I, I, I, P, I, L, P, P, P, P, I, P, P, P, P, I, P, I, I, I, I, I,
                                             I, I, I, F, I, P, P]},
         "delta.cu": {"ub_delta_prepare": [P, L, I, L, P, P, P, I, P, P, P, P, P, P, P, P, P, P, P, I, F, F, P],
                      "ub_conv_state_update": [P, L, I, L, P, P, P, I, I, I, P],
                      "ub_delta_scan": [P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
                      "ub_delta_finish": [P, P, P, P, I, I, I, I, F, P]},
+        "ssm.cu": {"ub_ssm_prepare": [P, L, I, L, P, P, P, P, I, P, P, P, P, P, P, P, P, I, P],
+                   "ub_ssm_conv_state_update": [P, L, I, L, P, P, P, P, I, P],
+                   "ub_ssm_scan": [P, P, P, P, P, P, P, P, I, I, I, I, I, P],
+                   "ub_ssm_finish": [P, P, L, I, L, P, P, P, I, I, I, F, F, P]},
         "sampling.cu": {"ub_sample": [P, L, P, I, I, P, P, P, P, P, U, P, P, I, P], "ub_sample_params_size": []},
     }.get(source, {})
     for name, args in sigs.items():
@@ -135,6 +145,57 @@ def embed(table, ids, out, status):
     assert table.is_contiguous() and table.shape[1] == width
     _check(_lib("basic.cu").ub_embed(_ptr(table), _code(table), _ptr(ids), _ptr(out), T, width,
                                      table.shape[0], _ptr(status), _stream()), "embed")
+
+
+def embed_pairs(table, pairs, ids, batch, last, out, status, scale, buckets, mul_prev, mul_cur):
+    """out[t, :] = scale * table[ids[t], :] + pairs[row, :], row = (previous token * mul_prev + ids[t] * mul_cur) mod
+    buckets, or ``buckets`` for a sequence's first token.  ``last`` (int32 [slots]): the token before the step's first
+    one, plus one (zero: none); the kernel moves it on to the step's last token."""
+    _need_cuda(table, pairs, ids, out, status, last)
+    T, width = out.shape
+    assert out.dtype == torch.float32 and ids.dtype == torch.int32 and out.is_contiguous() and last.dtype == torch.int32
+    assert table.is_contiguous() and pairs.is_contiguous() and table.shape[1] == width and pairs.shape == (buckets + 1, width)
+    assert table.dtype == pairs.dtype and last.is_contiguous()
+    _check(_lib("basic.cu").ub_embed_pairs(_ptr(table), _ptr(pairs), _code(table), _ptr(ids), _ptr(batch.tok_seq),
+                                           _ptr(batch.seq_start), _ptr(batch.seq_slot), _ptr(last), _ptr(out), T, width,
+                                           table.shape[0], float(scale), int(buckets), int(mul_prev), int(mul_cur),
+                                           _ptr(status), _stream()), "embed_pairs")
+
+
+def gated_add(g, bias, y, x, clear_y=False):
+    """x += sigmoid(g + bias) * y; x, y float32 [T, width]; g float32 [T, width] or [parts, T, width] (summed);
+    ``clear_y`` zeroes y behind the read."""
+    _need_cuda(g, bias, y, x)
+    T, width = x.shape
+    assert x.dtype == y.dtype == g.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == x.shape
+    if g.dim() == 3:
+        n_parts, part_stride = g.shape[0], g.stride(0)
+        assert g.shape[1:] == x.shape and g.stride(1) == width and g.stride(2) == 1
+    else:
+        n_parts, part_stride = 1, 0
+        assert g.shape == x.shape and g.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == width and bias.is_contiguous())
+    _check(_lib("basic.cu").ub_gated_add(_ptr(g), n_parts, part_stride, _ptr(bias), _ptr(y), _ptr(x), T, width,
+                                         1 if clear_y else 0, _stream()), "gated_add")
+
+
+def add_rows(x, a=None, v=None):
+    """x += a + v: ``a`` a float32 matrix of x's shape, ``v`` one float32 row added to every row."""
+    _need_cuda(x, a, v)
+    T, width = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    assert a is None or (a.dtype == torch.float32 and a.shape == x.shape and a.is_contiguous())
+    assert v is None or (v.dtype == torch.float32 and v.numel() == width and v.is_contiguous())
+    _check(_lib("basic.cu").ub_add_rows(_ptr(x), _ptr(a), _ptr(v), T, width, _stream()), "add_rows")
+
+
+def elem_gate(o, gate, scale=1.0):
+    """o[t, c] *= scale * sigmoid(gate[t, c]) in place; gate float32 [T, cols] (any row stride)."""
+    _need_cuda(o, gate)
+    T, cols = o.shape
+    assert o.stride(1) == 1 and gate.dtype == torch.float32 and gate.shape == (T, cols) and gate.stride(1) == 1
+    _check(_lib("basic.cu").ub_elem_gate(_ptr(o), _code(o), o.stride(0), _ptr(gate), gate.stride(0), T, cols, float(scale),
+                                         _stream()), "elem_gate")
 
 
 def rmsnorm(x, weight, out, eps, rows=None):
@@ -308,21 +369,30 @@ def gemm_simt(a, w, out, epilogue=EPI_STORE, w2=None):
 
 
 def attn_simple(q, k_cache, v_cache, out, tok_pos, tok_seq, table, ring, page, n_heads,
-                n_kv_heads, head_dim, window, scale, v_head_dim=None, block=None, gate=None):
+                n_kv_heads, head_dim, window, scale, v_head_dim=None, block=None, gate=None, keep_first=0, slopes=None,
+                sink=False, out_scale=1.0):
     """Attention of every token of the step over its sequence's cached keys and values.  ``v_head_dim``:
     the values' head size where it differs; ``block``: positions are masked in blocks of this many,
-    counted from the sequence's start; ``gate`` float32 [T, heads]: a head's output times its sigmoid."""
-    _need_cuda(q, k_cache, v_cache, out, table, gate)
+    counted from the sequence's start; ``gate`` float32 [T, heads] or [T, heads * value size]: the output
+    times its sigmoid, head by head or element by element; ``keep_first``: positions that stay visible
+    behind the window; ``slopes`` float32 [heads]: slope * distance is taken off a score; ``sink``: one
+    more term exp(0) in the softmax's sum; ``out_scale`` multiplies the output."""
+    _need_cuda(q, k_cache, v_cache, out, table, gate, slopes)
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype
     assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    gate_wide = 0
     if gate is not None:
-        assert gate.dtype == torch.float32 and gate.shape == (T, n_heads) and gate.stride(1) == 1
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape[0] == T
+        gate_wide = 0 if gate.shape[1] == n_heads and (v_head_dim or head_dim) != 1 else 1
+        assert gate.shape[1] == (n_heads * int(v_head_dim or head_dim) if gate_wide else n_heads)
+    assert slopes is None or (slopes.dtype == torch.float32 and slopes.numel() == n_heads and slopes.is_contiguous())
     _check(_lib("attn_simple.cu").ub_attn_simple(
         _ptr(q), q.stride(0), _code(q), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(out),
         out.stride(0), _ptr(tok_pos), _ptr(tok_seq), _ptr(table), table.shape[1], ring, page, T,
         n_heads, n_kv_heads, head_dim, int(window or 0), float(scale), int(v_head_dim or head_dim), int(block or 0),
-        _ptr(gate), gate.stride(0) if gate is not None else 0, _stream()), "attn_simple")
+        _ptr(gate), gate.stride(0) if gate is not None else 0, int(keep_first or 0), _ptr(slopes), 1 if sink else 0,
+        gate_wide, float(out_scale), _stream()), "attn_simple")
 
 
 def qkv_place(x, q_off, k_off, v_off, q_out, q_weight, k_weight, cos, sin, rotary_dim, tok_pos, tok_seq, k_cache,
@@ -354,6 +424,93 @@ def qkv_place(x, q_off, k_off, v_off, q_out, q_weight, k_weight, cos, sin, rotar
         _ptr(cos), _ptr(sin), rd, _ptr(tok_pos), _ptr(tok_seq), _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(table),
         table.shape[1], ring, page, T, n_heads, n_kv_heads, head_dim, int(v_head_dim), float(eps), int(g_off or 0),
         _ptr(gate_out), _stream()), "qkv_place")
+
+
+def qkv_place_rows(x, q_off, k_off, v_off, q_out, q_weight, k_weight, norm_whole, cos, sin, rotary_dim, interleaved, tok_pos,
+                   tok_seq, k_cache, v_cache, table, ring, page, n_heads, n_kv_heads, head_dim, v_head_dim, eps, g_off=None,
+                   gate_out=None):
+    """``qkv_place`` with one block a token: the norm may run over all query heads (and all key heads) at once
+    (``norm_whole``; weights [heads * head size]), the rotation may pair neighbouring columns (``interleaved``), and
+    the values may be any columns of the row (``v_off`` = ``k_off``: the keys before norm and rotation).
+    ``gate_out`` (float32 [T, any width], contiguous) receives that many columns from ``g_off`` on."""
+    _need_cuda(x, q_out, k_cache, v_cache, table)
+    if x.dim() == 3:
+        n_parts, T, part_stride, ldx = x.shape[0], x.shape[1], x.stride(0), x.stride(1)
+        assert x.stride(2) == 1
+    else:
+        n_parts, T, part_stride, ldx = 1, x.shape[0], 0, x.stride(0)
+        assert x.stride(1) == 1
+    assert q_out.stride(1) == 1 and q_out.shape == (T, n_heads * head_dim)
+    assert table.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    for v, n in ((q_weight, n_heads), (k_weight, n_kv_heads)):
+        assert v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == (n * head_dim if norm_whole else head_dim))
+    rd = int(rotary_dim or 0)
+    if cos is not None:
+        assert cos.dtype == torch.float32 and cos.is_contiguous() and cos.shape[1] == rd // 2 and sin.shape == cos.shape
+    g_width = 0
+    if gate_out is not None:
+        assert gate_out.dtype == torch.float32 and gate_out.is_contiguous() and gate_out.shape[0] == T and g_off is not None
+        g_width = gate_out.shape[1]
+    _check(_lib("attn_simple.cu").ub_qkv_place_rows(
+        _ptr(x), _code(x), ldx, n_parts, part_stride, int(q_off), -1 if k_off is None else int(k_off),
+        -1 if v_off is None else int(v_off), _ptr(q_out), _code(q_out), q_out.stride(0), _ptr(q_weight), _ptr(k_weight),
+        1 if norm_whole else 0, _ptr(cos), _ptr(sin), rd, 1 if interleaved else 0, _ptr(tok_pos), _ptr(tok_seq), _ptr(k_cache),
+        _ptr(v_cache), _code(k_cache), _ptr(table), table.shape[1], ring, page, T, n_heads, n_kv_heads, head_dim,
+        int(v_head_dim), float(eps), int(g_off or 0), g_width, _ptr(gate_out), _stream()), "qkv_place_rows")
+
+
+# ---------------------------------------------------------------------------------------
+# the state-space mixer (csrc/ssm.cu)
+def ssm_shape(H, P, N, G, taps, offs):
+    """The shape record the state-space kernels read: sizes and the first columns of z, x, B, C and dt in a
+    projection row."""
+    vals = [H, P, N, G, taps] + [int(o) for o in offs]
+    return (c_int * len(vals))(*vals)
+
+
+def ssm_prepare(p, shape, conv_w, conv_b, conv_state, dt_bias, a_log, batch, xbc, dtv, dec, update_state=False):
+    """p: the projection [z | x | B | C | dt] in float32.  Fills xbc (the convolution's channels after bias and SiLU),
+    dtv (step sizes) and dec (decays).  ``update_state`` (every sequence brings one token): the convolution's state
+    moves on in this kernel."""
+    _need_cuda(p, conv_w, conv_state, xbc, dtv, dec)
+    assert p.dtype == torch.float32
+    T, ldp, n_parts, part_stride = _parts_of(p)
+    for t in (conv_w, conv_b, conv_state, dt_bias, a_log, xbc, dtv, dec):
+        assert t is None or (t.dtype == torch.float32 and t.is_contiguous())
+    if update_state:
+        assert batch.n_seqs == T
+    _check(_lib("ssm.cu").ub_ssm_prepare(_ptr(p), ldp, n_parts, part_stride, shape, _ptr(conv_w), _ptr(conv_b), _ptr(conv_state),
+                                         1 if update_state else 0, _ptr(dt_bias), _ptr(a_log), _ptr(batch.tok_seq),
+                                         _ptr(batch.seq_start), _ptr(batch.seq_slot), _ptr(xbc), _ptr(dtv), _ptr(dec), T,
+                                         _stream()), "ssm_prepare")
+
+
+def ssm_conv_state_update(p, shape, conv_state, batch):
+    _need_cuda(p, conv_state)
+    assert p.dtype == torch.float32 and conv_state.dtype == torch.float32 and conv_state.is_contiguous()
+    _, ldp, n_parts, part_stride = _parts_of(p)
+    _check(_lib("ssm.cu").ub_ssm_conv_state_update(_ptr(p), ldp, n_parts, part_stride, shape, _ptr(conv_state),
+                                                   _ptr(batch.seq_start), _ptr(batch.seq_slot), batch.n_seqs, _stream()),
+           "ssm_conv_state_update")
+
+
+def ssm_scan(xbc, dtv, dec, d_skip, y, state, batch, H, P, N, G):
+    _need_cuda(xbc, dtv, dec, d_skip, y, state)
+    assert state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (H, N, P)
+    for t in (xbc, dtv, dec, d_skip, y):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    _check(_lib("ssm.cu").ub_ssm_scan(_ptr(xbc), _ptr(dtv), _ptr(dec), _ptr(d_skip), _ptr(y), _ptr(state), _ptr(batch.seq_start),
+                                      _ptr(batch.seq_slot), batch.n_seqs, H, P, N, G, _stream()), "ssm_scan")
+
+
+def ssm_finish(y, p, shape, weight, out, n_groups, eps, scale=1.0):
+    """out = v / rms(v) * weight * scale in ``n_groups`` equal parts of a row, v = y * silu(z), z from the projection."""
+    _need_cuda(y, p, weight, out)
+    assert y.dtype == torch.float32 and y.is_contiguous() and out.is_contiguous() and out.shape == y.shape
+    assert weight.dtype == torch.float32 and weight.is_contiguous() and weight.numel() == y.shape[1]
+    _, ldp, n_parts, part_stride = _parts_of(p)
+    _check(_lib("ssm.cu").ub_ssm_finish(_ptr(y), _ptr(p), ldp, n_parts, part_stride, shape, _ptr(weight), _ptr(out), _code(out),
+                                        y.shape[0], int(n_groups), float(eps), float(scale), _stream()), "ssm_finish")
 
 
 # ---------------------------------------------------------------------------------------

@@ -2,7 +2,10 @@
 from __future__ import annotations
 
 from ..kernels import ops
-from .base import Arrangement, register_part
+import torch
+
+from ..weights.spec import WeightSpec
+from .base import Arrangement, Entry, ResidualGate, register_part
 
 
 @register_part("arrangement", "pre_norm")
@@ -78,3 +81,104 @@ class NormAfterMixerOnly(_NormAfter):
 
     def __init__(self):
         pass
+
+
+@register_part("residual_gate", "sigmoid_linear")
+class SigmoidLinearGate(ResidualGate):
+    """x += sigmoid(W h + b) * y, element by element: a square projection of the sublayer's own input opens
+    or closes every channel of its result.  The projection's sums, the sigmoid and the sum into the stream
+    are float32 (for few tokens the product runs in K slices that the joining kernel adds up)."""
+
+    def __init__(self, width: int, bias: bool = True):
+        self.width, self.bias = int(width), bool(bias)
+        self.w = self.b = None
+
+    def weight_specs(self):
+        s = [WeightSpec("weight", (self.width, self.width))]
+        if self.bias:
+            s.append(WeightSpec("bias", (self.width,), "vector", ("normal", 0.5)))
+        return s
+
+    def bind(self, tensors, rt):
+        self.w = tensors["weight"].contiguous()
+        self.b = tensors["bias"].float().contiguous() if self.bias else None
+
+    def join(self, h, y, x, rt):
+        g = rt.matmul_parts(h, self.w)
+        if g is None:
+            g = rt.arena.alloc((h.shape[0], self.width), torch.float32)
+            rt.matmul(h, self.w, g)
+        rt.launches += 1
+        ops.gated_add(g, self.b, y, x, clear_y=True)
+
+
+class _ParallelGated(Arrangement):
+    """h = norm(x); x += gate_m(h) * mixer(h) + gate_f(h) * feed_forward(h): one norm, both sublayers read
+    its output, and each result passes a gate of its own (family ``residual_gate``) into the stream.  A
+    sublayer adds its output into the stream it is handed; here that is a cleared float32 buffer y, which
+    the gate's kernel folds into x and clears again.  y is kept from layer to layer of a pass."""
+
+    def _buffer(self, x, rt):
+        carry = getattr(rt, "_parallel_gated_carry", None)
+        if carry is not None and carry[0] == (rt.pass_id, x.data_ptr(), tuple(x.shape)):
+            return carry[1]
+        y = rt.arena.alloc(tuple(x.shape), x.dtype)
+        y.zero_()
+        rt._parallel_gated_carry = ((rt.pass_id, x.data_ptr(), tuple(x.shape)), y)
+        return y
+
+    def run(self, layer, x, batch, cache, rt):
+        y = self._buffer(x, rt)
+        mark = rt.arena.mark()
+        h = layer.norm.forward(x, rt)
+        inner = rt.arena.mark()
+        layer.mixer.forward(h, y, batch, cache, rt)
+        layer.mixer_gate.join(h, y, x, rt)
+        rt.arena.reset(inner)
+        ff = getattr(layer, "feed_forward", None)
+        if ff is not None:
+            ff.forward(h, y, batch, rt)
+            layer.feed_forward_gate.join(h, y, x, rt)
+        rt.arena.reset(mark)
+
+
+@register_part("arrangement", "parallel_gated")
+class ParallelGated(_ParallelGated):
+    roles = {"norm": "norm", "mixer": "mixer", "mixer_gate": "residual_gate", "feed_forward": "feed_forward",
+             "feed_forward_gate": "residual_gate"}
+
+    def __init__(self):
+        pass
+
+
+@register_part("arrangement", "parallel_gated_mixer_only")
+class ParallelGatedMixerOnly(_ParallelGated):
+    """The same layer without a feed-forward."""
+    roles = {"norm": "norm", "mixer": "mixer", "mixer_gate": "residual_gate"}
+
+    def __init__(self):
+        pass
+
+
+@register_part("entry", "pass_marker")
+class PassMarker(Entry):
+    """Before pass ``index`` of a group of layers that runs ``times`` times: x += step[index], one learned row
+    a pass (tensor ``step`` [times, width], shared by the passes' markers), and on every pass but the
+    first the embedding's output is added to the stream again."""
+
+    def __init__(self, width: int, times: int, index: int):
+        self.width, self.times, self.index = int(width), int(times), int(index)
+        if not (0 <= self.index < self.times):
+            raise ValueError("pass_marker: the pass's number must lie below the number of passes")
+        self.needs_embedding_output = self.index > 0
+        self.row = None
+
+    def weight_specs(self):
+        return [WeightSpec("step", (self.times, self.width), "vector", ("normal", 0.1))]
+
+    def bind(self, tensors, rt):
+        self.row = tensors["step"].float()[self.index].contiguous()
+
+    def forward(self, x, x0, rt):
+        rt.launches += 1
+        ops.add_rows(x, x0 if self.index > 0 else None, self.row)

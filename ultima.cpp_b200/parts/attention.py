@@ -31,6 +31,17 @@ class Attention(Mixer):
                   multiplied by its sigmoid before the output projection
       own_kv      False: the layer has no key and value tensors; its run reads another run's cache
                   (``Run.cache_from``) with its own queries
+      norm_whole  the q/k norm runs over all of a token's query heads at once (and over all its key heads),
+                  with one weight a column of the projection, instead of head by head
+      window + keep_first   behind a window of ``window`` positions the sequence's first ``keep_first``
+                  positions stay visible (the cache then holds every position)
+      distance_slope   a: head h (of H) takes 2^(-a (h + 1) / H) * (distance to the key) off every score
+      sink        the softmax's sum has one more term exp(0), which brings no value
+      values_are_keys   no value projection: a position's value is its key as projected, before norm and
+                  rotation (the cache holds both forms)
+      wide_gate   one more projection of the mixer's input, one number an output element; the heads' outputs
+                  are multiplied by its sigmoid before the output projection
+      out_scale   a constant on the mixer's output (applied to the heads' outputs, in float32)
     With any of them the layer runs on the general kernels (csrc/attn_simple.cu: placement of q, k, v from
     one fused projection row [q | k | v | gate], attention with the mask and the gate inside); a block
     mask alone, with equal head sizes, still takes the tensor-core attention kernels.
@@ -45,7 +56,9 @@ class Attention(Mixer):
     def __init__(self, width: int, n_heads: int, n_kv_heads: int, head_dim: int, qk_norm: bool,
                  eps: float, position: PartSpec | None, window: int | None = None,
                  scale: float | None = None, v_head_dim: int | None = None, block: int | None = None,
-                 head_gate: bool = False, own_kv: bool = True):
+                 head_gate: bool = False, own_kv: bool = True, norm_whole: bool = False, keep_first: int = 0,
+                 distance_slope: float | None = None, sink: bool = False, values_are_keys: bool = False,
+                 wide_gate: bool = False, out_scale: float = 1.0):
         if n_heads % n_kv_heads:
             raise ValueError("heads must be a multiple of kv heads")
         self.width, self.nh, self.nkv, self.hd = int(width), int(n_heads), int(n_kv_heads), int(head_dim)
@@ -59,25 +72,48 @@ class Attention(Mixer):
         if self.block is not None and self.block < 1:
             raise ValueError("attention: a block mask needs a positive block size")
         self.o_width, self.v_width = self.nh * self.hdv, self.nkv * self.hdv
-        self.general = self.hdv != self.hd or self.block is not None or self.head_gate or not self.own_kv
+        self.norm_whole, self.keep_first, self.sink = bool(norm_whole) and self.qk_norm, int(keep_first or 0), bool(sink)
+        self.distance_slope = float(distance_slope) if distance_slope is not None else None
+        self.values_are_keys, self.wide_gate, self.out_scale = bool(values_are_keys), bool(wide_gate), float(out_scale)
+        if self.values_are_keys and (self.hdv != self.hd or not self.own_kv):
+            raise ValueError("attention: values that are the keys have the keys' head size and belong to the layer itself")
+        if self.wide_gate and self.head_gate:
+            raise ValueError("attention: one gate a head or one an element, not both")
+        if self.keep_first and (self.window is None or self.block is not None):
+            raise ValueError("attention: kept first positions go with a window (and not with a block mask)")
+        if self.keep_first < 0:
+            raise ValueError("attention: keep_first must not be negative")
+        # what only the row-wise placement and the any-shape attention kernel take
+        interleaved = self.position is not None and bool(getattr(self.position, "interleaved", False))
+        self.extended = (self.norm_whole or self.keep_first > 0 or self.distance_slope is not None or self.sink
+                         or self.values_are_keys or self.wide_gate or self.out_scale != 1.0)
+        self.place_rows = self.norm_whole or self.values_are_keys or self.wide_gate or (self.extended and interleaved)
+        self.general = (self.hdv != self.hd or self.block is not None or self.head_gate or not self.own_kv
+                        or self.extended)
         self.wqkv = self.wo = self.q_norm = self.k_norm = None
 
     def weight_specs(self):
         s = [WeightSpec("q_proj.weight", (self.q_width, self.width))]
         if self.own_kv:
-            s += [WeightSpec("k_proj.weight", (self.kv_width, self.width)),
-                  WeightSpec("v_proj.weight", (self.v_width, self.width))]
+            s.append(WeightSpec("k_proj.weight", (self.kv_width, self.width)))
+            if not self.values_are_keys:
+                s.append(WeightSpec("v_proj.weight", (self.v_width, self.width)))
         s.append(WeightSpec("o_proj.weight", (self.width, self.o_width)))
         if self.qk_norm:
-            s.append(WeightSpec("q_norm.weight", (self.hd,), "vector", ("one_plus_normal", 0.05)))
+            s.append(WeightSpec("q_norm.weight", (self.q_width if self.norm_whole else self.hd,), "vector",
+                                ("one_plus_normal", 0.05)))
             if self.own_kv:
-                s.append(WeightSpec("k_norm.weight", (self.hd,), "vector", ("one_plus_normal", 0.05)))
+                s.append(WeightSpec("k_norm.weight", (self.kv_width if self.norm_whole else self.hd,), "vector",
+                                    ("one_plus_normal", 0.05)))
         if self.head_gate:
             s.append(WeightSpec("gate_proj.weight", (self.nh, self.width)))
+        if self.wide_gate:
+            s.append(WeightSpec("gate_proj.weight", (self.o_width, self.width)))
         return s
 
     def cache_need(self):
-        return KVNeed(self.nkv, self.hd, self.window, self.hdv if self.hdv != self.hd else None)
+        # kept first positions lie outside any ring of the window's size: the cache then holds all positions
+        return KVNeed(self.nkv, self.hd, None if self.keep_first else self.window, self.hdv if self.hdv != self.hd else None)
 
     def kernel_needs(self, run_dtype):
         from ..kernels import attn_tc, catalog
@@ -85,6 +121,8 @@ class Attention(Mixer):
             return [("attn_simple.cu", ())]
         if self.general:
             out = [("attn_simple.cu", ())]
+            if self.extended:
+                return out
             if self._fast_attention() and attn_tc.BLOCK_MASK:
                 out.append(attn_tc.target(self.hd))
                 if self.hd in catalog.TC_HEAD_DIMS:
@@ -100,7 +138,7 @@ class Attention(Mixer):
     def _fast_attention(self) -> bool:
         """Whether a general layer's attention itself can still go to the tensor-core kernels: equal head
         sizes of a kind they take; the block mask they know, the gate is applied behind them."""
-        return self.hdv == self.hd and self.hd % 16 == 0 and 16 <= self.hd <= 256
+        return self.hdv == self.hd and self.hd % 16 == 0 and 16 <= self.hd <= 256 and not self.extended
 
     def bind(self, tensors, rt):
         if (self.hd % 2 and not self.general) or self.hd > ops.MAX_HEAD_DIM or self.hdv > ops.MAX_HEAD_DIM:
@@ -108,8 +146,10 @@ class Attention(Mixer):
                              f"{ops.MAX_HEAD_DIM})")
         ws = [tensors["q_proj.weight"]]
         if self.own_kv:
-            ws += [tensors["k_proj.weight"], tensors["v_proj.weight"]]
-        if self.head_gate:
+            ws.append(tensors["k_proj.weight"])
+            if not self.values_are_keys:
+                ws.append(tensors["v_proj.weight"])
+        if self.head_gate or self.wide_gate:
             ws.append(tensors["gate_proj.weight"])
         if len({w.dtype for w in ws}) != 1:
             raise ValueError("q, k and v projections must share one element type")
@@ -124,8 +164,13 @@ class Attention(Mixer):
             if self.general and self.position.rotation() is None:
                 raise ValueError("attention: with a block mask, a gate, unequal head sizes or shared keys the "
                                  "position encoding must be a rotation of pairs")
-            if self.general and self.position.rotation().interleaved:
-                raise ValueError("attention: the general kernels rotate pairs (j, j + rotary_dim / 2) only")
+            if self.general and self.position.rotation().interleaved and not self.place_rows:
+                raise ValueError("attention: the head-wise placement kernel rotates pairs (j, j + rotary_dim / 2) only")
+        self.slopes = None
+        if self.distance_slope is not None:
+            h = torch.arange(1, self.nh + 1, dtype=torch.float64)
+            self.slopes = torch.pow(torch.tensor(2.0, dtype=torch.float64), -self.distance_slope * h / self.nh) \
+                .float().contiguous().to(rt.device)
 
     def _forward_general(self, h, residual, batch, cache, rt):
         """One product [q | k | v | gate] in float32, placement (norm, rotation, cache write), attention
@@ -142,13 +187,21 @@ class Attention(Mixer):
             rt.matmul(h, self.wqkv, x)
         q = rt.arena.alloc((T, self.q_width), rt.dtype)
         k_off = self.q_width if self.own_kv else None
-        v_off = self.q_width + self.kv_width if self.own_kv else None
-        g_off = self.q_width + (self.kv_width + self.v_width if self.own_kv else 0)
+        v_off = (k_off if self.values_are_keys else self.q_width + self.kv_width) if self.own_kv else None
+        g_off = self.q_width + ((self.kv_width + (0 if self.values_are_keys else self.v_width)) if self.own_kv else 0)
         gate = rt.arena.alloc((T, self.nh), torch.float32) if self.head_gate else None
+        if self.wide_gate:
+            gate = rt.arena.alloc((T, self.o_width), torch.float32)
         rt.launches += 1
-        ops.qkv_place(x, 0, k_off, v_off, q, self.q_norm, self.k_norm, rot.cos if rot else None,
-                      rot.sin if rot else None, rot.dim if rot else 0, batch.tok_pos, batch.tok_seq, kv.k, kv.v,
-                      kv.table, kv.ring, kv.page, self.nh, self.nkv, self.hd, self.hdv, self.eps, g_off, gate)
+        if self.place_rows:
+            ops.qkv_place_rows(x, 0, k_off, v_off, q, self.q_norm, self.k_norm, self.norm_whole, rot.cos if rot else None,
+                               rot.sin if rot else None, rot.dim if rot else 0, bool(rot.interleaved) if rot else False,
+                               batch.tok_pos, batch.tok_seq, kv.k, kv.v, kv.table, kv.ring, kv.page, self.nh, self.nkv,
+                               self.hd, self.hdv, self.eps, g_off, gate)
+        else:
+            ops.qkv_place(x, 0, k_off, v_off, q, self.q_norm, self.k_norm, rot.cos if rot else None,
+                          rot.sin if rot else None, rot.dim if rot else 0, batch.tok_pos, batch.tok_seq, kv.k, kv.v,
+                          kv.table, kv.ring, kv.page, self.nh, self.nkv, self.hd, self.hdv, self.eps, g_off, gate)
         o = rt.arena.alloc((T, self.o_width), rt.dtype)
         if self._fast_attention() and rt.attention_fast(q, kv, o, batch, self.nh, self.nkv, self.hd, self.scale,
                                                         self.block):
@@ -158,7 +211,8 @@ class Attention(Mixer):
         else:
             rt.launches += 1
             ops.attn_simple(q, kv.k, kv.v, o, batch.tok_pos, batch.tok_seq, kv.table, kv.ring, kv.page, self.nh,
-                            self.nkv, self.hd, kv.window, self.scale, v_head_dim=self.hdv, block=self.block, gate=gate)
+                            self.nkv, self.hd, self.window, self.scale, v_head_dim=self.hdv, block=self.block, gate=gate,
+                            keep_first=self.keep_first, slopes=self.slopes, sink=self.sink, out_scale=self.out_scale)
         rt.matmul(o, self.wo, residual, ops.EPI_ADD)
 
     def forward(self, h, residual, batch, cache, rt):

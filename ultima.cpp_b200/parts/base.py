@@ -35,7 +35,7 @@ def part(kind: str, **params) -> PartSpec:
     return PartSpec(kind, tuple(sorted(params.items())))
 
 
-FAMILIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head")
+FAMILIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "residual_gate", "entry")
 _TABLES: dict[str, dict[str, type]] = {f: {} for f in FAMILIES}
 
 
@@ -166,6 +166,26 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class ResidualGate(Part):
+    """What a sublayer's result passes on its way into the residual stream."""
+    graph_safe = True
+
+    def join(self, h, y, x, rt) -> None:
+        """x += gate(h) * y and y cleared; h: the layer's normed input (activations), x, y: float32 [T, width]."""
+        raise NotImplementedError
+
+
+class Entry(Part):
+    """What happens to the residual stream right before a run of the run list (``Run.entry``): a model
+    that runs some of its layers several times may mark each pass this way."""
+    graph_safe = True
+    needs_embedding_output = False        # True: ``forward`` wants the stream as the embedding left it
+
+    def forward(self, x, x0, rt) -> None:
+        """Update x (float32 [T, width]) in place; x0: the embedding's output, or None if not asked for."""
+        raise NotImplementedError
+
+
 class Arrangement(Part):
     """How a layer's parts stand around the residual stream.  ``roles`` names the parts a layer
     of this arrangement has, role -> family; the model builds exactly those, from the layer's
@@ -222,9 +242,11 @@ def layer(arrangement: PartSpec, prefix: str = "", names=(), **roles) -> LayerSp
 @dataclass(frozen=True)
 class Run:
     """One entry of the run list: run ``layer``; ``cache_from`` names an earlier entry (by its
-    index in the run list) whose cache this run reads instead of keeping its own."""
+    index in the run list) whose cache this run reads instead of keeping its own; ``entry`` names one
+    of the model's ``entries`` (by index), applied to the stream right before this run."""
     layer: int
     cache_from: Optional[int] = None
+    entry: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -244,6 +266,8 @@ class ModelSpec:
     # ((name a part asks for, name the file stores), ...): for checkpoints whose tensor names do not
     # follow "prefix + the part's own name" (names without ".weight", say)
     renames: tuple = ()
+    # ((PartSpec of the family "entry", tensor-name prefix), ...): see ``Run.entry``
+    entries: tuple = ()
 
     def stored_name(self, name: str) -> str:
         """The name under which the file holds the tensor a part calls ``name`` (prefix included)."""
@@ -259,6 +283,8 @@ class ModelSpec:
         for L in self.layers:
             for role, family in L.roles().items():
                 out.append((L.name_of(role), family, L.part(role)))
+        for ps, prefix in self.entries:
+            out.append((prefix, "entry", ps))
         out.append((self.final_norm_name, "norm", self.final_norm))
         out.append((self.head_name, "head", self.head))
         return out

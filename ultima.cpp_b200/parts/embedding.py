@@ -5,7 +5,7 @@ import torch
 
 from ..kernels import ops
 from ..weights.spec import WeightSpec
-from .base import Part, register_part
+from .base import Part, StateNeed, register_part
 
 
 @register_part("embedding", "token_table")
@@ -29,6 +29,41 @@ class TokenTable(Part):
         x = rt.arena.alloc((ids.numel(), self.width), torch.float32)
         rt.launches += 1
         ops.embed(self.table, ids, x, self.status)
+        return x
+
+
+@register_part("embedding", "token_table_hashed_pairs")
+class TokenTableHashedPairs(Part):
+    """x_t = scale * E[id_t, :] + P[r_t, :] with a second table P of ``buckets`` + 1 rows:
+    r_t = (id_{t-1} * mul_prev + id_t * mul_cur) mod buckets, and r = buckets for a sequence's first token.
+    The token before a step's first one is state of the sequence: one int32 a slot (the id plus one; zero
+    means none yet), which the kernel reads and moves on, so a decode step that takes its ids from the
+    device needs nothing of the host."""
+
+    def __init__(self, vocab_size: int, width: int, scale: float, buckets: int, mul_prev: int, mul_cur: int):
+        self.vocab_size, self.width, self.scale = int(vocab_size), int(width), float(scale)
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        if self.buckets < 1:
+            raise ValueError("token_table_hashed_pairs: at least one bucket is needed")
+        self.table = self.pairs = None
+
+    def weight_specs(self):
+        return [WeightSpec("weight", (self.vocab_size, self.width)),
+                WeightSpec("pairs", (self.buckets + 1, self.width))]
+
+    def cache_need(self):
+        return StateNeed((1,), "int32")
+
+    def bind(self, tensors, rt):
+        self.table = tensors["weight"].contiguous()
+        self.pairs = tensors["pairs"].to(self.table.dtype).contiguous()
+        self.status = rt.status[0:1]
+
+    def forward_step(self, batch, cache, rt):
+        x = rt.arena.alloc((batch.tok_ids.numel(), self.width), torch.float32)
+        rt.launches += 1
+        ops.embed_pairs(self.table, self.pairs, batch.tok_ids, batch, cache.state, x, self.status, self.scale, self.buckets,
+                        self.mul_prev, self.mul_cur)
         return x
 
 

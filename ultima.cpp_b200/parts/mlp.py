@@ -100,3 +100,12 @@ class GatedClamped(FeedForward):
         rt.launches += 1
         ops.glu_clamped(gu, a, self.limit, self.alpha, self.shift)
         rt.matmul(a, self.wd, residual, ops.EPI_ADD)
+
+
+@register_part("feed_forward", "gated_relu")
+class GatedReLU(GatedClamped):
+    """down(max(gate(h), 0) * up(h)), no biases: the clamped gate product at its limits (no clamp, the
+    sigmoid as steep as it gets, no shift), so it runs as the same two launches."""
+
+    def __init__(self, width: int, inner: int):
+        super().__init__(width, inner, limit=float("inf"), alpha=float("inf"), shift=0.0)
