@@ -334,7 +334,8 @@ class Engine:
             self.cache.reserve(s, b + len(t))
         B = len(slots)
         tables = self.cache.tables(slots)
-        decode = self.use_graphs and all(len(t) == 1 for t in new_tokens) and list(want_rows) == list(range(B))
+        decode = self.use_graphs and all(len(t) == 1 for t in new_tokens) and list(want_rows) == list(range(B)) \
+            and self.model.tap is None                     # (a tap reads the stream on the host: no capture)
         if decode:
             logits = self._decode_pass(slots, new_tokens, before, want_rows, tables, ids_dev)
         else:
