@@ -118,9 +118,12 @@ __device__ __forceinline__ void weighted_values(float (*o)[4], const float (*s)[
 
 // One step of the running softmax over the masked scores of NT key groups; scores come in raw
 // (q.k) and leave as probabilities relative to the new maximum.  c = scale * log2(e).
-template <int NT>
+// EXT: behind a window the sequence's first ``keep_first`` positions stay visible, and row r takes
+// row_slope[r] (a slope in units of log2) times its distance to the key off the score.
+template <int NT, bool EXT = false>
 __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float* m, float* l, float c,
-                                             const int* row_pos, bool const* row_ok, int key_pos0, int window, int lane) {
+                                             const int* row_pos, bool const* row_ok, int key_pos0, int window, int lane,
+                                             int keep_first = 0, const float* row_slope = nullptr) {
     float mx[2] = {-INFINITY, -INFINITY};
     const int row_lo[2] = {span_lo(row_pos[0], window), span_lo(row_pos[1], window)};
 #pragma unroll
@@ -129,8 +132,14 @@ __device__ __forceinline__ void softmax_step(float (*s)[4], float (*o)[4], float
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
             const int kp = key_pos0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-            const bool ok = row_ok[r] && kp <= row_pos[r] && kp >= row_lo[r];
-            const float v = ok ? s[nt][e] * c : -INFINITY;
+            bool ok = row_ok[r] && kp <= row_pos[r] && kp >= row_lo[r];
+            float v;
+            if constexpr (EXT) {
+                ok = row_ok[r] && kp <= row_pos[r] && (kp >= row_lo[r] || kp < keep_first);
+                v = ok ? fmaf(-row_slope[r], (float)(row_pos[r] - kp), s[nt][e] * c) : -INFINITY;
+            } else {
+                v = ok ? s[nt][e] * c : -INFINITY;
+            }
             s[nt][e] = v;
             mx[r] = fmaxf(mx[r], v);
         }

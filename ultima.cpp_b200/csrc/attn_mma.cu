@@ -27,11 +27,31 @@ struct AttnParams {
     float c;                                  // scale * log2(e)
     float* part_o; float* part_ml;            // decode with several slices
     int n_slices;
+    // the extended kernels (EXT) only: positions kept visible behind the window, a sink in the softmax's sum,
+    // one slope a head (times log2(e)) for the bias by distance, a constant on the output, and one gate an
+    // output element (float32 [tokens, heads * HD], row stride g_stride), whose sigmoid multiplies the output
+    int keep_first, sink;
+    const float* slopes;
+    float out_scale;
+    const float* gate; long long g_stride;
+};
+
+// The tiles of 64 keys a query range reads, in order: with kept first positions, the tiles that hold them and lie
+// before the window's first tile, then the window's tiles t_lo .. t_hi.
+struct TileList {
+    int n_kept, t_lo, n;
+    __device__ __forceinline__ TileList(int keep_first, int t_lo_, int t_hi) {
+        n_kept = keep_first > 0 ? min(t_lo_, (keep_first + KT - 1) / KT) : 0;
+        t_lo = t_lo_;
+        n = n_kept + (t_hi - t_lo_ + 1);
+    }
+    __device__ __forceinline__ int tile(int i) const { return i < n_kept ? i : t_lo + (i - n_kept); }
 };
 
 // ---------------------------------------------------------------------------------------
 // prefill: grid (row tiles of the longest sequence, sequences, KV heads)
 // ---------------------------------------------------------------------------------------
+template <bool EXT>
 __global__ void __launch_bounds__(NTHREADS)
 attn_prefill_kernel(AttnParams p, PagedKV c) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -75,13 +95,20 @@ attn_prefill_kernel(AttnParams p, PagedKV c) {
 #pragma unroll
     for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float row_slope[2] = {0.f, 0.f};
+    if constexpr (EXT) {
+        if (p.sink) { m[0] = m[1] = 0.f; l[0] = l[1] = 1.f; }         // the sink: a key with score 0 and no value
+        if (p.slopes) { row_slope[0] = p.slopes[kvh * G + row_g[0]]; row_slope[1] = p.slopes[kvh * G + row_g[1]]; }
+    }
+    const TileList tiles(EXT ? p.keep_first : 0, t_lo, t_hi);
 
-    load_kv_tile(Ks, Vs, p.kc, p.vc, c, seq, kvh, t_lo * KT, last_pos, tid);
+    load_kv_tile(Ks, Vs, p.kc, p.vc, c, seq, kvh, tiles.tile(0) * KT, last_pos, tid);
     cp_async_commit();
-    for (int t = t_lo; t <= t_hi; ++t) {
-        const int buf = (t - t_lo) & 1;
-        if (t < t_hi) {
-            load_kv_tile(Ks + (buf ^ 1) * KT * LDS, Vs + (buf ^ 1) * KT * LDS, p.kc, p.vc, c, seq, kvh, (t + 1) * KT, last_pos, tid);
+    for (int i = 0; i < tiles.n; ++i) {
+        const int t = tiles.tile(i);
+        const int buf = i & 1;
+        if (i + 1 < tiles.n) {
+            load_kv_tile(Ks + (buf ^ 1) * KT * LDS, Vs + (buf ^ 1) * KT * LDS, p.kc, p.vc, c, seq, kvh, tiles.tile(i + 1) * KT, last_pos, tid);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
@@ -92,24 +119,32 @@ attn_prefill_kernel(AttnParams p, PagedKV c) {
         const bf16* V = Vs + buf * KT * LDS;
         float s[8][4];
         scores<8>(s, Qs, warp * 16, K, 0, lane);
-        softmax_step<8>(s, o, m, l, p.c, row_pos, row_ok, t * KT, p.window, lane);
+        softmax_step<8, EXT>(s, o, m, l, p.c, row_pos, row_ok, t * KT, p.window, lane, p.keep_first, row_slope);
         weighted_values<8>(o, s, V, 0, lane);
         __syncthreads();                             // the buffer is loaded again two tiles on
     }
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         if (!row_ok[r]) continue;
-        const float inv = 1.0f / l[r];
-        bf16* dst = p.out + (long long)(q0 + row_tok[r]) * p.o_stride + (long long)(kvh * G + row_g[r]) * HD + (lane & 3) * 2;
+        const float inv = (EXT ? p.out_scale : 1.0f) / l[r];
+        const long long col = (long long)(kvh * G + row_g[r]) * HD + (lane & 3) * 2;
+        bf16* dst = p.out + (long long)(q0 + row_tok[r]) * p.o_stride + col;
+        const float* gt = (EXT && p.gate) ? p.gate + (long long)(q0 + row_tok[r]) * p.g_stride + col : nullptr;
 #pragma unroll
-        for (int dt = 0; dt < DTILES; ++dt)
-            *reinterpret_cast<uint32_t*>(dst + dt * 8) = pack_bf16(o[dt][2 * r] * inv, o[dt][2 * r + 1] * inv);
+        for (int dt = 0; dt < DTILES; ++dt) {
+            float a = o[dt][2 * r] * inv, b = o[dt][2 * r + 1] * inv;
+            if (EXT && gt) { a *= 1.0f / (1.0f + __expf(-gt[dt * 8])); b *= 1.0f / (1.0f + __expf(-gt[dt * 8 + 1])); }
+            *reinterpret_cast<uint32_t*>(dst + dt * 8) = pack_bf16(a, b);
+        }
     }
 }
+
+
 
 // ---------------------------------------------------------------------------------------
 // decode: one new token a sequence; grid (slices, sequences, KV heads); group <= 16
 // ---------------------------------------------------------------------------------------
+template <bool EXT>
 __global__ void __launch_bounds__(NTHREADS)
 attn_decode_kernel(AttnParams p, PagedKV c) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -125,10 +160,9 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
     const int row = p.seq_start[seq];              // the sequence's one token
     const int pos = p.seq_before[seq];             // its position; keys [lo, pos]
     const int lo = span_lo(pos, p.window);
-    const int t_first = lo / KT, t_last = pos / KT;
-    const int n_tiles = t_last - t_first + 1;
-    const int per = (n_tiles + p.n_slices - 1) / p.n_slices;
-    const int t_lo = t_first + slice * per, t_hi = min(t_last, t_lo + per - 1);
+    const TileList tiles(EXT ? p.keep_first : 0, lo / KT, pos / KT);
+    const int per = (tiles.n + p.n_slices - 1) / p.n_slices;
+    const int t_lo = slice * per, t_hi = min(tiles.n - 1, t_lo + per - 1);        // places in the list of tiles
 
     constexpr int CH = HD / 8;
     for (int i = tid; i < 16 * CH; i += NTHREADS) {
@@ -143,13 +177,20 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
 #pragma unroll
     for (int dt = 0; dt < DTILES; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f;
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float row_slope[2] = {0.f, 0.f};
+    if constexpr (EXT) {
+        if (p.slopes) {
+            if ((lane >> 2) < G) row_slope[0] = p.slopes[kvh * G + (lane >> 2)];
+            if ((lane >> 2) + 8 < G) row_slope[1] = p.slopes[kvh * G + (lane >> 2) + 8];
+        }
+    }
 
     // a ring of DSTAGES tiles: DSTAGES - 1 tiles are on their way while one is used.  One group of
     // copies is committed for every tile slot, empty past the end, so the count to wait for is fixed.
 #pragma unroll
     for (int i = 0; i < DSTAGES - 1; ++i) {
         if (t_lo + i <= t_hi)
-            load_kv_tile(Ks + i * KT * LDS, Vs + i * KT * LDS, p.kc, p.vc, c, seq, kvh, (t_lo + i) * KT, pos, tid);
+            load_kv_tile(Ks + i * KT * LDS, Vs + i * KT * LDS, p.kc, p.vc, c, seq, kvh, tiles.tile(t_lo + i) * KT, pos, tid);
         cp_async_commit();
     }
     for (int t = t_lo; t <= t_hi; ++t) {
@@ -157,14 +198,14 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
         const int ahead = t + DSTAGES - 1;
         if (ahead <= t_hi) {
             const int nb = (ahead - t_lo) % DSTAGES;
-            load_kv_tile(Ks + nb * KT * LDS, Vs + nb * KT * LDS, p.kc, p.vc, c, seq, kvh, ahead * KT, pos, tid);
+            load_kv_tile(Ks + nb * KT * LDS, Vs + nb * KT * LDS, p.kc, p.vc, c, seq, kvh, tiles.tile(ahead) * KT, pos, tid);
         }
         cp_async_commit();
         cp_async_wait<DSTAGES - 1>();
         __syncthreads();
         float s[2][4];
         scores<2>(s, Qs, 0, Ks + buf * KT * LDS, warp * 16, lane);
-        softmax_step<2>(s, o, m, l, p.c, row_pos, row_ok, t * KT + warp * 16, p.window, lane);
+        softmax_step<2, EXT>(s, o, m, l, p.c, row_pos, row_ok, tiles.tile(t) * KT + warp * 16, p.window, lane, p.keep_first, row_slope);
         weighted_values<2>(o, s, Vs + buf * KT * LDS, warp * 16, lane);
         __syncthreads();                             // the slot is filled again at the next step
     }
@@ -188,7 +229,9 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
         float mm = -INFINITY;
 #pragma unroll
         for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red[(w * 16 + g) * RS + HD]);
-        float acc = 0.f, ll = 0.f;
+        const bool with_sink = EXT && p.sink && p.n_slices == 1;      // (with several slices the sink joins in attn_combine)
+        if (with_sink) mm = fmaxf(mm, 0.f);
+        float acc = 0.f, ll = with_sink ? exp2f(-mm) : 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float mw = red[(w * 16 + g) * RS + HD];
@@ -198,7 +241,12 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
         }
         const int head = kvh * G + g;
         if (p.n_slices == 1) {
-            p.out[(long long)row * p.o_stride + (long long)head * HD + d] = __float2bfloat16_rn(acc / ll);
+            float v = acc / ll;
+            if constexpr (EXT) {
+                v *= p.out_scale;
+                if (p.gate) v *= 1.0f / (1.0f + __expf(-p.gate[(long long)row * p.g_stride + (long long)head * HD + d]));
+            }
+            p.out[(long long)row * p.o_stride + (long long)head * HD + d] = __float2bfloat16_rn(v);
         } else {
             const long long pi = ((long long)seq * p.nh + head) * p.n_slices + slice;
             p.part_o[pi * HD + d] = acc;
@@ -208,6 +256,7 @@ attn_decode_kernel(AttnParams p, PagedKV c) {
 }
 
 // merge the slices of a decode step: grid (sequences * heads), HD threads (rounded up to a warp)
+template <bool EXT>
 __global__ void attn_combine_kernel(AttnParams p) {
     pdl_trigger();
     pdl_wait();
@@ -216,14 +265,23 @@ __global__ void attn_combine_kernel(AttnParams p) {
     const long long base = (long long)sh * p.n_slices;
     float mm = -INFINITY;
     for (int s = 0; s < p.n_slices; ++s) mm = fmaxf(mm, p.part_ml[(base + s) * 2]);
-    float acc = 0.f, ll = 0.f;
+    const bool with_sink = EXT && p.sink;
+    if (with_sink) mm = fmaxf(mm, 0.f);
+    float acc = 0.f, ll = with_sink ? exp2f(-mm) : 0.f;
     for (int s = 0; s < p.n_slices; ++s) {
         const float ms = p.part_ml[(base + s) * 2];
         const float f = ms == -INFINITY ? 0.f : exp2f(ms - mm);
         ll += f * p.part_ml[(base + s) * 2 + 1];
         if (d < HD) acc += f * p.part_o[(base + s) * HD + d];
     }
-    if (d < HD) p.out[(long long)p.seq_start[seq] * p.o_stride + (long long)head * HD + d] = __float2bfloat16_rn(acc / ll);
+    if (d < HD) {
+        float v = acc / ll;
+        if constexpr (EXT) {
+            v *= p.out_scale;
+            if (p.gate) v *= 1.0f / (1.0f + __expf(-p.gate[(long long)p.seq_start[seq] * p.g_stride + (long long)head * HD + d]));
+        }
+        p.out[(long long)p.seq_start[seq] * p.o_stride + (long long)head * HD + d] = __float2bfloat16_rn(v);
+    }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -231,27 +289,15 @@ UB_API int ub_attn_head_dim() { return HD; }
 
 // mode 0: prefill kernel (any numbers of new tokens), mode 1: decode kernel (one new token for
 // every sequence, group <= 16).  part_o: float32 [n_seqs, nh, n_slices, HD], part_ml: [.., 2].
-UB_API int ub_attn_mma(int mode, const void* q, long long q_stride, void* out, long long o_stride, const void* kcache,
-                       const void* vcache, const int* seq_start, const int* seq_before, const int* table,
-                       int pages_per_seq, int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window,
-                       float scale, int n_slices, float* part_o, float* part_ml, cudaStream_t st) {
-    if (n_seqs <= 0) return 0;
-    if (page != KT || ring % page != 0 || nh % nkv != 0 || (q_stride % 8) != 0 || (o_stride % 2) != 0) return UB_ERR_ARG;
-    if (((uintptr_t)q & 15) || ((uintptr_t)out & 3) || ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15)) return UB_ERR_ARG;
-    if (n_seqs > 65535 || nkv > 65535) return UB_ERR_ARG;
-    PagedKV c{table, pages_per_seq, ring, page, nkv, HD};
-    AttnParams p;
-    p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.o_stride = o_stride;
-    p.kc = (const bf16*)kcache; p.vc = (const bf16*)vcache; p.seq_start = seq_start; p.seq_before = seq_before;
-    p.nh = nh; p.group = nh / nkv; p.window = window; p.c = scale * 1.4426950408889634f;
-    p.part_o = part_o; p.part_ml = part_ml; p.n_slices = n_slices < 1 ? 1 : n_slices;
+template <bool EXT>
+static int launch_mma(int mode, AttnParams p, PagedKV c, int n_seqs, int max_new, int nkv, cudaStream_t st) {
     static bool attr_done = false;
     const size_t sm_pre = (size_t)(64 + 4 * KT) * LDS * sizeof(bf16);
     const size_t sm_kv = (size_t)2 * DSTAGES * KT * LDS * sizeof(bf16), sm_red = (size_t)64 * (HD + 2) * sizeof(float);
     const size_t sm_dec = (size_t)16 * LDS * sizeof(bf16) + (ATTN_ALIAS ? (sm_kv > sm_red ? sm_kv : sm_red) : sm_kv + sm_red);
     if (!attr_done) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_pre);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_dec);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_pre);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attn_decode_kernel<EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm_dec);
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
@@ -259,21 +305,66 @@ UB_API int ub_attn_mma(int mode, const void* q, long long q_stride, void* out, l
         const int tiles = (max_new * p.group + 63) / 64;
         if (tiles < 1) return 0;
         dim3 grid(tiles, n_seqs, nkv);
-        cudaError_t e = ub_launch_dependent(attn_prefill_kernel, grid, dim3(NTHREADS), sm_pre, st, p, c);
+        cudaError_t e = ub_launch_dependent(attn_prefill_kernel<EXT>, grid, dim3(NTHREADS), sm_pre, st, p, c);
         if (e != cudaSuccess) return (int)e;
     } else {
         if (p.group > 16 || max_new != 1) return UB_ERR_ARG;
-        if (p.n_slices > 1 && (!part_o || !part_ml)) return UB_ERR_ARG;
+        if (p.n_slices > 1 && (!p.part_o || !p.part_ml)) return UB_ERR_ARG;
         dim3 grid(p.n_slices, n_seqs, nkv);
-        cudaError_t e = ub_launch_dependent(attn_decode_kernel, grid, dim3(NTHREADS), sm_dec, st, p, c);
+        cudaError_t e = ub_launch_dependent(attn_decode_kernel<EXT>, grid, dim3(NTHREADS), sm_dec, st, p, c);
         if (e != cudaSuccess) return (int)e;
         if (p.n_slices > 1) {
-            e = ub_launch_dependent(attn_combine_kernel, dim3(n_seqs * nh), dim3(((HD + 31) / 32) * 32), 0, st, p);
+            e = ub_launch_dependent(attn_combine_kernel<EXT>, dim3(n_seqs * p.nh), dim3(((HD + 31) / 32) * 32), 0, st, p);
             if (e != cudaSuccess) return (int)e;
         }
     }
     UB_LAUNCH_CHECK();
     return 0;
+}
+
+static int fill_params(AttnParams& p, const void* q, long long q_stride, void* out, long long o_stride, const void* kcache,
+                       const void* vcache, const int* seq_start, const int* seq_before, int ring, int page, int n_seqs,
+                       int nh, int nkv, int window, float scale, int n_slices, float* part_o, float* part_ml) {
+    if (page != KT || ring % page != 0 || nh % nkv != 0 || (q_stride % 8) != 0 || (o_stride % 2) != 0) return UB_ERR_ARG;
+    if (((uintptr_t)q & 15) || ((uintptr_t)out & 3) || ((uintptr_t)kcache & 15) || ((uintptr_t)vcache & 15)) return UB_ERR_ARG;
+    if (n_seqs > 65535 || nkv > 65535) return UB_ERR_ARG;
+    p.q = (const bf16*)q; p.q_stride = q_stride; p.out = (bf16*)out; p.o_stride = o_stride;
+    p.kc = (const bf16*)kcache; p.vc = (const bf16*)vcache; p.seq_start = seq_start; p.seq_before = seq_before;
+    p.nh = nh; p.group = nh / nkv; p.window = window; p.c = scale * 1.4426950408889634f;
+    p.part_o = part_o; p.part_ml = part_ml; p.n_slices = n_slices < 1 ? 1 : n_slices;
+    p.keep_first = 0; p.sink = 0; p.slopes = nullptr; p.out_scale = 1.0f; p.gate = nullptr; p.g_stride = 0;
+    return 0;
+}
+
+UB_API int ub_attn_mma(int mode, const void* q, long long q_stride, void* out, long long o_stride, const void* kcache,
+                       const void* vcache, const int* seq_start, const int* seq_before, const int* table,
+                       int pages_per_seq, int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window,
+                       float scale, int n_slices, float* part_o, float* part_ml, cudaStream_t st) {
+    if (n_seqs <= 0) return 0;
+    AttnParams p;
+    if (int rc = fill_params(p, q, q_stride, out, o_stride, kcache, vcache, seq_start, seq_before, ring, page, n_seqs, nh, nkv,
+                             window, scale, n_slices, part_o, part_ml)) return rc;
+    PagedKV c{table, pages_per_seq, ring, page, nkv, HD};
+    return launch_mma<false>(mode, p, c, n_seqs, max_new, nkv, st);
+}
+
+// The same two kernels with the further options: ``keep_first`` positions that stay visible behind the window
+// (window > 0), ``sink`` (one more term exp(0) in the softmax's sum), ``slopes`` (float32 [nh], already times
+// log2(e): slope * distance is taken off a score), ``out_scale``, and ``gate`` (float32 [tokens, nh * HD], row
+// stride g_stride: the output times its sigmoid, element by element).
+UB_API int ub_attn_mma_ext(int mode, const void* q, long long q_stride, void* out, long long o_stride, const void* kcache,
+                           const void* vcache, const int* seq_start, const int* seq_before, const int* table,
+                           int pages_per_seq, int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window,
+                           float scale, int n_slices, float* part_o, float* part_ml, int keep_first, int sink,
+                           const float* slopes, float out_scale, const float* gate, long long g_stride, cudaStream_t st) {
+    if (n_seqs <= 0) return 0;
+    if (keep_first < 0 || window < 0 || (keep_first > 0 && window == 0)) return UB_ERR_ARG;
+    AttnParams p;
+    if (int rc = fill_params(p, q, q_stride, out, o_stride, kcache, vcache, seq_start, seq_before, ring, page, n_seqs, nh, nkv,
+                             window, scale, n_slices, part_o, part_ml)) return rc;
+    p.keep_first = keep_first; p.sink = sink ? 1 : 0; p.slopes = slopes; p.out_scale = out_scale; p.gate = gate; p.g_stride = g_stride;
+    PagedKV c{table, pages_per_seq, ring, page, nkv, HD};
+    return launch_mma<true>(mode, p, c, n_seqs, max_new, nkv, st);
 }
 
 
@@ -554,7 +645,7 @@ static int decode_tma_launch(const void* map_k, const void* map_v, const void* q
                                         *(const CUtensorMap*)map_k, *(const CUtensorMap*)map_v, tp);
     if (e != cudaSuccess) return (int)e;
     if (p.n_slices > 1) {
-        e = ub_launch_dependent(attn_combine_kernel, dim3(n_seqs * nh), dim3(((HD + 31) / 32) * 32), 0, st, p);
+        e = ub_launch_dependent(attn_combine_kernel<false>, dim3(n_seqs * nh), dim3(((HD + 31) / 32) * 32), 0, st, p);
         if (e != cudaSuccess) return (int)e;
     }
     return 0;

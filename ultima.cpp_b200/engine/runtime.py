@@ -173,6 +173,19 @@ class Runtime:
         attn_tc.attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, self, block=block)
         return True
 
+    def attention_ext(self, q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, **options) -> bool:
+        """The tensor-core attention kernels with the attention part's further options (window with kept first
+        positions, sink, bias by distance, output scale, a gate an element; see ``attn_tc.attention_ext``), where
+        they take the case; False where they do not, and nothing was launched."""
+        if not (self.use_tensor_cores and q.dtype == torch.bfloat16):
+            return False
+        from ..kernels import attn_tc
+        if not attn_tc.accepts(q, kv, head_dim, n_heads, n_kv_heads) or not attn_tc.EXTENDED:
+            return False
+        self.launches += 1
+        attn_tc.attention_ext(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, self, **options)
+        return True
+
     def attention(self, q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale):
         self.launches += 1
         if self.use_tensor_cores and q.dtype == torch.bfloat16:

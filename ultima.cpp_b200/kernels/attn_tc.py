@@ -29,6 +29,8 @@ def lib(head_dim: int):
                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_float, c_int, c_void_p, c_void_p, c_void_p]
         L.ub_attn_mma.restype = c_int
+        L.ub_attn_mma_ext.argtypes = L.ub_attn_mma.argtypes[:-1] + [c_int, c_int, c_void_p, c_float, c_void_p, c_longlong, c_void_p]
+        L.ub_attn_mma_ext.restype = c_int
         L.ub_attn_head_dim.restype = c_int
         if L.ub_attn_head_dim() != head_dim:
             raise KernelError(f"attention library was built for head size {L.ub_attn_head_dim()}, not {head_dim}")
@@ -199,6 +201,8 @@ def decode_from_qkv(qkv, q_norm, k_norm, cos, sin, eps, kv, out, batch, n_heads,
 # The kernels take the mask as one integer: w > 0, the last w positions; w < 0, blocks of -w positions
 # counted from the sequence's start (a token sees the earlier tokens of its own block); 0, everything before.
 BLOCK_MASK = True
+# ULTIMA_ATTN_EXTENDED=0: layers with the further options (see ``attention_ext``) stay on the any-shape kernel
+EXTENDED = _os.environ.get("ULTIMA_ATTN_EXTENDED", "1") != "0"
 
 
 def _mask_arg(kv, block) -> int:
@@ -250,3 +254,31 @@ def attention(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, slice
                        kv.page, batch.n_seqs, batch.max_new, n_heads, n_kv_heads, mask, float(scale),
                        n_slices, _ptr(part_o), _ptr(part_ml), _stream())
     _check(rc, "attn_mma")
+
+
+def attention_ext(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, window=None, keep_first=0, sink=False,
+                  slopes_log2=None, out_scale=1.0, gate=None, slices: int | None = None):
+    """The mma.sync kernels (prompts, and single tokens with groups of up to 16 heads) with the further options of
+    the attention part: ``window`` with ``keep_first`` positions kept visible behind it, ``sink``, ``slopes_log2``
+    (float32 [heads], slope * log2(e)), ``out_scale`` and ``gate`` (float32 [T, heads * head size], contiguous: one
+    sigmoid gate an output element).  The cache holds every position or is a ring of the window's size."""
+    L = lib(head_dim)
+    assert out.dtype == torch.bfloat16 and out.stride(1) == 1
+    group = n_heads // n_kv_heads
+    decode = batch.max_new == 1 and group <= 16
+    part_o = part_ml = None
+    n_slices = 1
+    if decode:
+        reach = (int(window) + int(keep_first or 0)) if window else None
+        n_slices = slices or decode_slices(batch.n_seqs, n_kv_heads, batch.max_after, reach)
+        if n_slices > 1:
+            part_o = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, head_dim), torch.float32)
+            part_ml = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, 2), torch.float32)
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (q.shape[0], n_heads * head_dim)
+    rc = L.ub_attn_mma_ext(1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), _ptr(kv.v),
+                           _ptr(batch.seq_start), _ptr(batch.seq_before), _ptr(kv.table), kv.table.shape[1], kv.ring,
+                           kv.page, batch.n_seqs, batch.max_new, n_heads, n_kv_heads, int(window or 0), float(scale),
+                           n_slices, _ptr(part_o), _ptr(part_ml), int(keep_first or 0), 1 if sink else 0, _ptr(slopes_log2),
+                           float(out_scale), _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
+    _check(rc, "attn_mma_ext")

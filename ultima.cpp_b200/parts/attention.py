@@ -122,6 +122,8 @@ class Attention(Mixer):
         if self.general:
             out = [("attn_simple.cu", ())]
             if self.extended:
+                if self._fast_extended() and attn_tc.EXTENDED:
+                    out.append(attn_tc.target(self.hd))
                 return out
             if self._fast_attention() and attn_tc.BLOCK_MASK:
                 out.append(attn_tc.target(self.hd))
@@ -139,6 +141,12 @@ class Attention(Mixer):
         """Whether a general layer's attention itself can still go to the tensor-core kernels: equal head
         sizes of a kind they take; the block mask they know, the gate is applied behind them."""
         return self.hdv == self.hd and self.hd % 16 == 0 and 16 <= self.hd <= 256 and not self.extended
+
+    def _fast_extended(self) -> bool:
+        """Whether a layer with the further options can go to the tensor-core kernels that know them (mma.sync):
+        equal head sizes of a kind they take, no block mask, no gate a head."""
+        return (self.extended and self.hdv == self.hd and self.hd % 16 == 0 and 16 <= self.hd <= 256
+                and self.block is None and not self.head_gate and self.own_kv)
 
     def bind(self, tensors, rt):
         if (self.hd % 2 and not self.general) or self.hd > ops.MAX_HEAD_DIM or self.hdv > ops.MAX_HEAD_DIM:
@@ -166,11 +174,12 @@ class Attention(Mixer):
                                  "position encoding must be a rotation of pairs")
             if self.general and self.position.rotation().interleaved and not self.place_rows:
                 raise ValueError("attention: the head-wise placement kernel rotates pairs (j, j + rotary_dim / 2) only")
-        self.slopes = None
+        self.slopes = self.slopes_log2 = None
         if self.distance_slope is not None:
             h = torch.arange(1, self.nh + 1, dtype=torch.float64)
-            self.slopes = torch.pow(torch.tensor(2.0, dtype=torch.float64), -self.distance_slope * h / self.nh) \
-                .float().contiguous().to(rt.device)
+            slopes = torch.pow(torch.tensor(2.0, dtype=torch.float64), -self.distance_slope * h / self.nh)
+            self.slopes = slopes.float().contiguous().to(rt.device)
+            self.slopes_log2 = (slopes * math.log2(math.e)).float().contiguous().to(rt.device)   # for kernels that work in powers of two
 
     def _forward_general(self, h, residual, batch, cache, rt):
         """One product [q | k | v | gate] in float32, placement (norm, rotation, cache write), attention
@@ -203,8 +212,12 @@ class Attention(Mixer):
                           rot.sin if rot else None, rot.dim if rot else 0, batch.tok_pos, batch.tok_seq, kv.k, kv.v,
                           kv.table, kv.ring, kv.page, self.nh, self.nkv, self.hd, self.hdv, self.eps, g_off, gate)
         o = rt.arena.alloc((T, self.o_width), rt.dtype)
-        if self._fast_attention() and rt.attention_fast(q, kv, o, batch, self.nh, self.nkv, self.hd, self.scale,
-                                                        self.block):
+        if self._fast_extended() and rt.attention_ext(q, kv, o, batch, self.nh, self.nkv, self.hd, self.scale, window=self.window,
+                                                      keep_first=self.keep_first, sink=self.sink, slopes_log2=self.slopes_log2,
+                                                      out_scale=self.out_scale, gate=gate):
+            pass
+        elif self._fast_attention() and rt.attention_fast(q, kv, o, batch, self.nh, self.nkv, self.hd, self.scale,
+                                                          self.block):
             if gate is not None:
                 rt.launches += 1
                 ops.head_gate(o, gate, self.nh, self.hdv)
