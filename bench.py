@@ -469,7 +469,35 @@ def _kernel_times(run_once):
     return {k: [v[0], round(v[1], 1)] for k, v in sorted(out.items(), key=lambda kv: -kv[1][1])}
 
 
+def tinuzen_config(z):
+    """Layers in fours: windowed attention, then three times attention beside a state-space mixer; one pass."""
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+           "mask": {"size": 1024, "keep_first": 4}}
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["dim"], "scale": z["dim"] ** -0.5,
+            "rot": {"base": 10000.0, "dims": z["dim"]}}
+    right = {"heads": z["width"] // 64, "vdim": 64, "state": 128, "groups": 2, "conv": 4, "norm_groups": 2}
+    mlp = {"kind": "dense", "ff": z["ff"]}
+    layers = []
+    for i in range(z["layers"]):
+        if i % 4 == 0:
+            layers.append({"type": "attention", "mixer": dict(att), "mlp": dict(mlp)})
+        else:
+            layers.append({"type": "parallel", "mlp": dict(mlp),
+                           "mixer": {"left": dict(left), "right": dict(right), "left_scale": 1.2, "right_scale": 0.9}})
+    return {"architecture": "Tinuzen", "vocab": z["vocab"], "width": z["width"], "norm": {"eps": 1e-5},
+            "embedding": {"scale": 16.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
+            "loop": {"start": 0, "stop": z["layers"], "times": 1}, "layers": layers}
+
+
 def sugizen_times(args):
+    return design_times(args, "sugizen", (("sugizen", sugizen_config), ("qwen3", qwen3_config_like)))
+
+
+def tinuzen_times(args):
+    return design_times(args, "tinuzen", (("tinuzen", tinuzen_config), ("sugizen", sugizen_config), ("qwen3", qwen3_config_like)))
+
+
+def design_times(args, only, models):
     import numpy as np
     import torch
     import ultima_b200 as u
@@ -484,8 +512,8 @@ def sugizen_times(args):
     clocks.start()
     for size, z in SUGIZEN_SIZES.items():
         result[size] = {}
-        for model, cfg_dict in (("sugizen", sugizen_config(z)), ("qwen3", qwen3_config_like(z))):
-            cfg = u.config_from_dict(cfg_dict)
+        for model, make in models:
+            cfg = u.config_from_dict(make(z))
             spec = u.model_spec_for(cfg)
             tensors = random_tensors_on_device(spec.weight_specs(), 0, torch.bfloat16, dev)
             engine = Engine(spec, tensors, dtype="bfloat16", max_tokens=B * (args.prompt + 256) + P + 64, max_seqs=B + 1,
@@ -537,7 +565,7 @@ def sugizen_times(args):
             print(f"[bench] {size} {model}: prefill {prefill_ms:.2f} ms, decode {decode_ms * 1e3:.0f} us", file=sys.stderr, flush=True)
             del engine
             torch.cuda.empty_cache()
-    print(json.dumps({"only": "sugizen", "dtype": "bf16", "data": "synthetic", "peaks": peaks(), "clocks": clocks.stop(),
+    print(json.dumps({"only": only, "dtype": "bf16", "data": "synthetic", "peaks": peaks(), "clocks": clocks.stop(),
                       "sizes": result}))
     return 0
 
@@ -900,14 +928,15 @@ def main():
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in config)")
-    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample", "attention", "peaks", "sugizen"],
+    ap.add_argument("--only", default="all", choices=["all", "prefill", "decode", "timeline", "timeline-prefill", "sample", "attention", "peaks", "sugizen", "tinuzen"],
                     help="a part of the run only (for profiling); the JSON line then holds that part. "
                          "timeline: every kernel of a decode step with its begin and end inside the graph "
                          "(timeline-prefill: of a prompt); "
                          "sample: the sampling kernel alone, option by option; attention: the prompt attention alone; "
                          "peaks: this GPU's copy bandwidth and library bfloat16 product, the denominators' kind; "
                          "sugizen: prompt and decode throughput of the Sugizen design beside Qwen3 at equal layer sizes "
-                         "(two widths, eight layers), with every kernel's time in a prompt and in a decode step")
+                         "(two widths, eight layers), with every kernel's time in a prompt and in a decode step; "
+                         "tinuzen: the same for the Tinuzen design beside Sugizen and Qwen3")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences of the decode step")
     ap.add_argument("--fast-fill", action="store_true", help="do not run the prompts; mark the cache as filled")
     ap.add_argument("--prompt", type=int, default=PROMPT, help="positions each sequence holds before the timed steps")
@@ -937,6 +966,8 @@ def main():
         return measured_peaks()
     if args.only == "sugizen":
         return sugizen_times(args)
+    if args.only == "tinuzen":
+        return tinuzen_times(args)
     if args.config != "8b":
         return run_other(args)
     return run_ours(args)

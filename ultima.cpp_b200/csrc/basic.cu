@@ -825,16 +825,18 @@ UB_API int ub_embed_pairs(const void* table, const void* pairs, int table_dtype,
 // gate's sums ([T, width], or the sum of ``n_parts`` partial results ``part_stride`` apart), b its bias
 // (optional).  ``clear_y``: y, which sublayers add their output into, is zeroed behind the read.
 // ---------------------------------------------------------------------------------------
-__global__ void gated_add_kernel(const float* __restrict__ g, int n_parts, long long part_stride, const float* __restrict__ b,
-                                 float* __restrict__ y, float* __restrict__ x, long long n, int width, int clear_y) {
+__global__ void gated_add_kernel(const float* __restrict__ g, long long ldg, int n_parts, long long part_stride,
+                                 const float* __restrict__ b, float* __restrict__ y, float* __restrict__ x, long long n, int width,
+                                 int clear_y) {
     pdl_trigger();
     pdl_wait();
     const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i >= n) return;
     const int c = (int)(i % width);
-    float4 s = *reinterpret_cast<const float4*>(g + i);
+    const float* gp = g + (i / width) * ldg + c;
+    float4 s = *reinterpret_cast<const float4*>(gp);
     for (int p = 1; p < n_parts; ++p) {
-        const float4 q = *reinterpret_cast<const float4*>(g + p * part_stride + i);
+        const float4 q = *reinterpret_cast<const float4*>(gp + p * part_stride);
         s.x += q.x; s.y += q.y; s.z += q.z; s.w += q.w;
     }
     if (b) { s.x += b[c]; s.y += b[c + 1]; s.z += b[c + 2]; s.w += b[c + 3]; }
@@ -848,31 +850,34 @@ __global__ void gated_add_kernel(const float* __restrict__ g, int n_parts, long 
     if (clear_y) *reinterpret_cast<float4*>(y + i) = make_float4(0.f, 0.f, 0.f, 0.f);
 }
 
-__global__ void gated_add_scalar_kernel(const float* __restrict__ g, int n_parts, long long part_stride, const float* __restrict__ b,
-                                        float* __restrict__ y, float* __restrict__ x, long long n, int width, int clear_y) {
+__global__ void gated_add_scalar_kernel(const float* __restrict__ g, long long ldg, int n_parts, long long part_stride,
+                                        const float* __restrict__ b, float* __restrict__ y, float* __restrict__ x, long long n,
+                                        int width, int clear_y) {
     pdl_trigger();
     pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
+    const float* gp = g + (i / width) * ldg + i % width;
     float s = 0.f;
-    for (int p = 0; p < n_parts; ++p) s += g[p * part_stride + i];
+    for (int p = 0; p < n_parts; ++p) s += gp[p * part_stride];
     if (b) s += b[i % width];
     x[i] = fmaf(y[i], 1.0f / (1.0f + expf(-s)), x[i]);
     if (clear_y) y[i] = 0.f;
 }
 
-UB_API int ub_gated_add(const float* g, int n_parts, long long part_stride, const float* b, float* y, float* x, int n_rows,
-                        int width, int clear_y, cudaStream_t st) {
+// g: row stride ldg (the gate's sums may be a column range of a wider product)
+UB_API int ub_gated_add(const float* g, long long ldg, int n_parts, long long part_stride, const float* b, float* y, float* x,
+                        int n_rows, int width, int clear_y, cudaStream_t st) {
     const long long n = (long long)n_rows * width;
     if (n <= 0) return 0;
     if (n_parts < 1) return UB_ERR_ARG;
     cudaError_t e;
-    if (width % 4 == 0 && part_stride % 4 == 0 && (((uintptr_t)g | (uintptr_t)y | (uintptr_t)x) & 15) == 0)
-        e = ub_launch_dependent(gated_add_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, g, n_parts, part_stride, b,
-                                y, x, n, width, clear_y);
-    else
-        e = ub_launch_dependent(gated_add_scalar_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, g, n_parts, part_stride,
+    if (width % 4 == 0 && ldg % 4 == 0 && part_stride % 4 == 0 && (((uintptr_t)g | (uintptr_t)y | (uintptr_t)x) & 15) == 0)
+        e = ub_launch_dependent(gated_add_kernel, dim3((unsigned)((n / 4 + 255) / 256)), dim3(256), 0, st, g, ldg, n_parts, part_stride,
                                 b, y, x, n, width, clear_y);
+    else
+        e = ub_launch_dependent(gated_add_scalar_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, g, ldg, n_parts,
+                                part_stride, b, y, x, n, width, clear_y);
     return (int)e;
 }
 

@@ -92,17 +92,31 @@ __global__ void ssm_conv_state_update_kernel(const float* __restrict__ p, SsmSha
 }
 
 // The recurrence.  A block of 128 threads takes 16 value channels of one head of one sequence; eight lanes
-// hold one column of S, lane l the state channels l, l + 8, ...  Tokens come through shared memory a few
-// at a time (two buffers: the next tokens are fetched while these are worked on).  The state's update
-// does not wait for the read-out: a token costs two operations a state element and three exchanges.
-template <int R>
+// hold one column of S, lane l the state channels of the float4 chunks l, l + 8, ...: the lanes of a column read
+// consecutive bytes of shared memory in one instruction.  Tokens come through shared memory a stage at a time,
+// the next stage asked for (cp.async) while this one is worked on.  The state's update does not wait for the
+// read-out: a token costs two operations a state element and three exchanges.
+__device__ __forceinline__ void ssm_cp4(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void ssm_cp16(float* dst, const float* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
+// VEC: N, P and the row stride are multiples of 4 and xbc starts on a 16-byte boundary: 16-byte copies.
+template <int R, bool VEC>
 __global__ void __launch_bounds__(128)
 ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, const float* __restrict__ dec,
                 const float* __restrict__ Dw, float* __restrict__ y, float* __restrict__ S,
                 const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int H, int P, int N, int G) {
-    constexpr int LANES = 8, COLS = 16, TT = 8, NP = LANES * R;
-    __shared__ float sB[2][TT][NP], sC[2][TT][NP];
-    __shared__ float sx[2][TT][COLS], sdt[2][TT], sa[2][TT];
+    static_assert(R % 4 == 0, "a lane holds whole float4 chunks");
+    constexpr int LANES = 8, COLS = 16, NP = LANES * R, NC = R / 4;
+    constexpr int TT = NP <= 64 ? 16 : 8;                 // tokens a stage
+    __shared__ __align__(16) float sB[2][TT][NP], sC[2][TT][NP];
+    __shared__ __align__(16) float sx[2][TT][COLS];
+    __shared__ float sdt[2][TT], sa[2][TT];
     pdl_trigger();
     pdl_wait();
     const int tid = threadIdx.x, col = tid / LANES, l = tid % LANES;
@@ -115,54 +129,95 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
     float s[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int n = i * LANES + l;
+        const int n = ((i >> 2) * LANES + l) * 4 + (i & 3);
         s[i] = (n < N && j < P) ? Sh[(long long)n * P + j] : 0.f;
     }
+    // channels past the sizes are zeros that no copy ever touches
+    for (int idx = tid; idx < 2 * TT * NP; idx += blockDim.x)
+        if (idx % NP >= N) { (&sB[0][0][0])[idx] = 0.f; (&sC[0][0][0])[idx] = 0.f; }
+    for (int idx = tid; idx < 2 * TT * COLS; idx += blockDim.x)
+        if (blockIdx.x * COLS + idx % COLS >= P) (&sx[0][0][0])[idx] = 0.f;
     const float dh = Dw[h];
+    const float* brow = xbc + H * P + g * N;
+    const float* xrow = xbc + h * P + blockIdx.x * COLS;
     auto fetch = [&](int base, int buf) {
         const int cnt = min(TT, t1 - base);
-        for (int idx = tid; idx < cnt * NP; idx += blockDim.x) {
-            const int tt = idx / NP, n = idx % NP;
-            const float* rowp = xbc + (long long)(base + tt) * C + H * P + g * N;
-            sB[buf][tt][n] = n < N ? rowp[n] : 0.f;
-            sC[buf][tt][n] = n < N ? rowp[G * N + n] : 0.f;
+        if (VEC) {
+            const int n4 = N >> 2;
+            for (int idx = tid; idx < cnt * n4; idx += blockDim.x) {
+                const int tt = idx / n4, n = (idx % n4) * 4;
+                const float* rowp = brow + (long long)(base + tt) * C;
+                ssm_cp16(&sB[buf][tt][n], rowp + n);
+                ssm_cp16(&sC[buf][tt][n], rowp + G * N + n);
+            }
+            if (tid < cnt * (COLS / 4)) {
+                const int tt = tid / (COLS / 4), cc = (tid % (COLS / 4)) * 4;
+                if (blockIdx.x * COLS + cc < P) ssm_cp16(&sx[buf][tt][cc], xrow + (long long)(base + tt) * C + cc);
+            }
+        } else {
+            for (int idx = tid; idx < cnt * N; idx += blockDim.x) {
+                const int tt = idx / N, n = idx % N;
+                const float* rowp = brow + (long long)(base + tt) * C;
+                ssm_cp4(&sB[buf][tt][n], rowp + n);
+                ssm_cp4(&sC[buf][tt][n], rowp + G * N + n);
+            }
+            for (int idx = tid; idx < cnt * COLS; idx += blockDim.x) {
+                const int tt = idx / COLS, cc = idx % COLS;
+                if (blockIdx.x * COLS + cc < P) ssm_cp4(&sx[buf][tt][cc], xrow + (long long)(base + tt) * C + cc);
+            }
         }
-        for (int idx = tid; idx < cnt * COLS; idx += blockDim.x) {
-            const int tt = idx / COLS, cc = idx % COLS;
-            const int jj = blockIdx.x * COLS + cc;
-            sx[buf][tt][cc] = jj < P ? xbc[(long long)(base + tt) * C + h * P + jj] : 0.f;
-        }
-        if (tid < cnt) {
-            sdt[buf][tid] = dtv[(long long)(base + tid) * H + h];
-            sa[buf][tid] = dec[(long long)(base + tid) * H + h];
-        }
+        if (tid >= 64 && tid < 64 + cnt) ssm_cp4(&sdt[buf][tid - 64], dtv + (long long)(base + tid - 64) * H + h);
+        if (tid >= 96 && tid < 96 + cnt) ssm_cp4(&sa[buf][tid - 96], dec + (long long)(base + tid - 96) * H + h);
+        asm volatile("cp.async.commit_group;" ::: "memory");
     };
+    __syncthreads();                                       // the constants above are in place before any copy lands beside them
     fetch(t0, 0);
-    __syncthreads();
     int buf = 0;
     for (int base = t0; base < t1; base += TT, buf ^= 1) {
         const int cnt = min(TT, t1 - base);
-        if (base + TT < t1) fetch(base + TT, buf ^ 1);     // (its readers passed the barrier at the end of the last round)
-        for (int tt = 0; tt < cnt; ++tt) {
+        if (base + TT < t1) {
+            fetch(base + TT, buf ^ 1);                     // (that buffer's readers passed the barrier at the end of the last round)
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        }
+        __syncthreads();
+        auto token = [&](int tt) {
+            const float4* B4 = reinterpret_cast<const float4*>(sB[buf][tt]);
+            const float4* C4 = reinterpret_cast<const float4*>(sC[buf][tt]);
             const float a = sa[buf][tt];
             const float xv = sx[buf][tt][col];
             const float u = sdt[buf][tt] * xv;
-            float part = 0.f;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < R; ++i) {
-                s[i] = fmaf(a, s[i], sB[buf][tt][i * LANES + l] * u);
-                part = fmaf(s[i], sC[buf][tt][i * LANES + l], part);
+            for (int c = 0; c < NC; ++c) {
+                const float4 bv = B4[c * LANES + l], cv = C4[c * LANES + l];
+                s[4 * c + 0] = fmaf(a, s[4 * c + 0], bv.x * u);
+                s[4 * c + 1] = fmaf(a, s[4 * c + 1], bv.y * u);
+                s[4 * c + 2] = fmaf(a, s[4 * c + 2], bv.z * u);
+                s[4 * c + 3] = fmaf(a, s[4 * c + 3], bv.w * u);
+                part[0] = fmaf(s[4 * c + 0], cv.x, part[0]);
+                part[1] = fmaf(s[4 * c + 1], cv.y, part[1]);
+                part[2] = fmaf(s[4 * c + 2], cv.z, part[2]);
+                part[3] = fmaf(s[4 * c + 3], cv.w, part[3]);
             }
-            part += __shfl_xor_sync(0xffffffffu, part, 1);
-            part += __shfl_xor_sync(0xffffffffu, part, 2);
-            part += __shfl_xor_sync(0xffffffffu, part, 4);
-            if (l == 0 && j < P) y[((long long)(base + tt) * H + h) * P + j] = fmaf(dh, xv, part);
+            float sum = (part[0] + part[1]) + (part[2] + part[3]);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            if (l == 0 && j < P) y[((long long)(base + tt) * H + h) * P + j] = fmaf(dh, xv, sum);
+        };
+        if (cnt == TT) {
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt) token(tt);
+        } else {
+            for (int tt = 0; tt < cnt; ++tt) token(tt);
         }
-        __syncthreads();
+        __syncthreads();                                   // this buffer is asked for again in the next round
     }
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int n = i * LANES + l;
+        const int n = ((i >> 2) * LANES + l) * 4 + (i & 3);
         if (n < N && j < P) Sh[(long long)n * P + j] = s[i];
     }
 }
@@ -234,9 +289,11 @@ UB_API int ub_ssm_scan(const float* xbc, const float* dtv, const float* dec, con
     if (H <= 0 || G <= 0 || H % G || P <= 0 || N <= 0 || N > 256 || H > 65535 || n_seqs > 65535) return UB_ERR_ARG;
     const dim3 grid((P + 15) / 16, H, n_seqs), block(128);
     const int per = (N + 7) / 8;
+    const bool vec = N % 4 == 0 && P % 4 == 0 && (((uintptr_t)xbc) & 15) == 0;
     cudaError_t e;
-#define GO(RR) e = ub_launch_dependent(ssm_scan_kernel<RR>, grid, block, 0, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G)
-    if (per <= 2) GO(2); else if (per <= 4) GO(4); else if (per <= 8) GO(8); else if (per <= 16) GO(16); else GO(32);
+#define GO(RR) e = vec ? ub_launch_dependent(ssm_scan_kernel<RR, true>, grid, block, 0, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G) \
+                       : ub_launch_dependent(ssm_scan_kernel<RR, false>, grid, block, 0, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G)
+    if (per <= 4) GO(4); else if (per <= 8) GO(8); else if (per <= 16) GO(16); else GO(32);
 #undef GO
     return (int)e;
 }

@@ -110,7 +110,7 @@ def _declare(lib, source: str) -> None:
             "ub_add_into": [P, P, I, L, P],
             "ub_fill_normal": [P, I, L, U, F, F, P],
             "ub_embed_pairs": [P, P, I, P, P, P, P, P, P, I, I, I, F, I, L, L, P, P],
-            "ub_gated_add": [P, I, L, P, P, P, I, I, I, P],
+            "ub_gated_add": [P, L, I, L, P, P, P, I, I, I, P],
             "ub_add_rows": [P, P, P, I, I, P],
             "ub_elem_gate": [P, I, L, P, L, I, I, F, P],
         },
@@ -163,19 +163,19 @@ def embed_pairs(table, pairs, ids, batch, last, out, status, scale, buckets, mul
 
 
 def gated_add(g, bias, y, x, clear_y=False):
-    """x += sigmoid(g + bias) * y; x, y float32 [T, width]; g float32 [T, width] or [parts, T, width] (summed);
-    ``clear_y`` zeroes y behind the read."""
+    """x += sigmoid(g + bias) * y; x, y float32 [T, width]; g float32 [T, width] or [parts, T, width] (summed), rows of
+    any stride (a column range of a wider product); ``clear_y`` zeroes y behind the read."""
     _need_cuda(g, bias, y, x)
     T, width = x.shape
     assert x.dtype == y.dtype == g.dtype == torch.float32 and x.is_contiguous() and y.is_contiguous() and y.shape == x.shape
     if g.dim() == 3:
-        n_parts, part_stride = g.shape[0], g.stride(0)
-        assert g.shape[1:] == x.shape and g.stride(1) == width and g.stride(2) == 1
+        n_parts, part_stride, ldg = g.shape[0], g.stride(0), g.stride(1)
+        assert g.shape[1:] == x.shape and g.stride(2) == 1
     else:
-        n_parts, part_stride = 1, 0
-        assert g.shape == x.shape and g.is_contiguous()
+        n_parts, part_stride, ldg = 1, 0, g.stride(0)
+        assert g.shape == x.shape and g.stride(1) == 1
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == width and bias.is_contiguous())
-    _check(_lib("basic.cu").ub_gated_add(_ptr(g), n_parts, part_stride, _ptr(bias), _ptr(y), _ptr(x), T, width,
+    _check(_lib("basic.cu").ub_gated_add(_ptr(g), ldg, n_parts, part_stride, _ptr(bias), _ptr(y), _ptr(x), T, width,
                                          1 if clear_y else 0, _stream()), "gated_add")
 
 

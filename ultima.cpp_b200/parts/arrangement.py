@@ -103,11 +103,29 @@ class SigmoidLinearGate(ResidualGate):
         self.w = tensors["weight"].contiguous()
         self.b = tensors["bias"].float().contiguous() if self.bias else None
 
-    def join(self, h, y, x, rt):
-        g = rt.matmul_parts(h, self.w)
+    @staticmethod
+    def _sums(h, w, rt):
+        g = rt.matmul_parts(h, w)
         if g is None:
-            g = rt.arena.alloc((h.shape[0], self.width), torch.float32)
-            rt.matmul(h, self.w, g)
+            g = rt.arena.alloc((h.shape[0], w.shape[0]), torch.float32)
+            rt.matmul(h, w, g)
+        return g
+
+    @classmethod
+    def fused_sums(cls, gates, h, rt):
+        """One product for all of a layer's gates: their matrices stacked (made once, kept on the first gate)."""
+        if len(gates) < 2 or any(type(g) is not cls or g.w.dtype != gates[0].w.dtype or g.width != gates[0].width for g in gates):
+            return None
+        first = gates[0]
+        if getattr(first, "_stacked_for", None) != tuple(id(g) for g in gates):
+            first._stacked = torch.cat([g.w for g in gates], dim=0).contiguous()
+            first._stacked_for = tuple(id(g) for g in gates)
+        s = cls._sums(h, first._stacked, rt)
+        w = first.width
+        return [s[..., i * w:(i + 1) * w] for i in range(len(gates))]
+
+    def join(self, h, y, x, rt, sums=None):
+        g = sums if sums is not None else self._sums(h, self.w, rt)
         rt.launches += 1
         ops.gated_add(g, self.b, y, x, clear_y=True)
 
@@ -131,14 +149,16 @@ class _ParallelGated(Arrangement):
         y = self._buffer(x, rt)
         mark = rt.arena.mark()
         h = layer.norm.forward(x, rt)
+        ff = getattr(layer, "feed_forward", None)
+        gates = [layer.mixer_gate] + ([layer.feed_forward_gate] if ff is not None else [])
+        sums = type(gates[0]).fused_sums(gates, h, rt) or [None] * len(gates)       # one product for both gates where they can
         inner = rt.arena.mark()
         layer.mixer.forward(h, y, batch, cache, rt)
-        layer.mixer_gate.join(h, y, x, rt)
+        gates[0].join(h, y, x, rt, sums[0])
         rt.arena.reset(inner)
-        ff = getattr(layer, "feed_forward", None)
         if ff is not None:
             ff.forward(h, y, batch, rt)
-            layer.feed_forward_gate.join(h, y, x, rt)
+            gates[1].join(h, y, x, rt, sums[1])
         rt.arena.reset(mark)
 
 

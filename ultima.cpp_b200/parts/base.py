@@ -170,9 +170,16 @@ class ResidualGate(Part):
     """What a sublayer's result passes on its way into the residual stream."""
     graph_safe = True
 
-    def join(self, h, y, x, rt) -> None:
-        """x += gate(h) * y and y cleared; h: the layer's normed input (activations), x, y: float32 [T, width]."""
+    def join(self, h, y, x, rt, sums=None) -> None:
+        """x += gate(h) * y and y cleared; h: the layer's normed input (activations), x, y: float32 [T, width].
+        ``sums``: what ``fused_sums`` made for this gate, if the arrangement called it."""
         raise NotImplementedError
+
+    @classmethod
+    def fused_sums(cls, gates, h, rt):
+        """Gates of one layer that read the same input may make their sums together: a list with one entry a gate
+        (handed back to each ``join`` as ``sums``), or None if these gates cannot."""
+        return None
 
 
 class Entry(Part):
