@@ -91,9 +91,11 @@ __global__ void ssm_conv_state_update_kernel(const float* __restrict__ p, SsmSha
     for (int k = 0; k < K; ++k) st[(long long)k * C + c] = tmp[k];
 }
 
-// The recurrence.  A block of 128 threads takes 16 value channels of one head of one sequence; eight lanes
-// hold one column of S, lane l the state channels of the float4 chunks l, l + 8, ...: the lanes of a column read
-// consecutive bytes of shared memory in one instruction.  Tokens come through shared memory a stage at a time,
+// The recurrence.  A block of 256 threads takes 256 / LANES value channels of one head of one sequence; LANES
+// (8, 16 or 32, by the state's size alone, so that the order of every sum is the same whatever the batch) lanes
+// hold one column of S, lane l the state channels of the float4 chunks l, l + LANES, ...: the lanes of a column
+// read consecutive bytes of shared memory in one instruction.  More lanes a column mean more warps with fewer
+// values each: the kernel is bound by the latency of a token's chain, which many warps hide.  Tokens come through shared memory a stage at a time,
 // the next stage asked for (cp.async) while this one is worked on.  The state's update does not wait for the
 // read-out: a token costs two operations a state element and three exchanges.
 __device__ __forceinline__ void ssm_cp4(float* dst, const float* src) {
@@ -106,13 +108,13 @@ __device__ __forceinline__ void ssm_cp16(float* dst, const float* src) {
 }
 
 // VEC: N, P and the row stride are multiples of 4 and xbc starts on a 16-byte boundary: 16-byte copies.
-template <int R, bool VEC>
-__global__ void __launch_bounds__(128)
+template <int R, int LANES, bool VEC>
+__global__ void __launch_bounds__(256)
 ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, const float* __restrict__ dec,
                 const float* __restrict__ Dw, float* __restrict__ y, float* __restrict__ S,
                 const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int H, int P, int N, int G) {
     static_assert(R % 4 == 0, "a lane holds whole float4 chunks");
-    constexpr int LANES = 8, COLS = 16, NP = LANES * R, NC = R / 4;
+    constexpr int COLS = 256 / LANES, NP = LANES * R, NC = R / 4;
     constexpr int TT = NP <= 64 ? 16 : 8;                 // tokens a stage
     __shared__ __align__(16) float sB[2][TT][NP], sC[2][TT][NP];
     __shared__ __align__(16) float sx[2][TT][COLS];
@@ -202,9 +204,8 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
                 part[3] = fmaf(s[4 * c + 3], cv.w, part[3]);
             }
             float sum = (part[0] + part[1]) + (part[2] + part[3]);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-            sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+#pragma unroll
+            for (int w = 1; w < LANES; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
             if (l == 0 && j < P) y[((long long)(base + tt) * H + h) * P + j] = fmaf(dh, xv, sum);
         };
         if (cnt == TT) {
@@ -222,29 +223,41 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
     }
 }
 
-// One warp a (token, part of the row): v = y silu(z); v / rms(v) * w * scale.
+// One block a (token, part of the row): v = y silu(z); v / rms(v) * w * scale.  A thread keeps up to eight of
+// its values between the two passes; a part wider than that is read twice.
 template <typename TO>
 __global__ void __launch_bounds__(128)
 ssm_finish_kernel(const float* __restrict__ y, const float* __restrict__ p, SsmShape s, const float* __restrict__ w,
                   TO* __restrict__ out, int n_tokens, int n_groups, float eps, float scale) {
+    __shared__ float red[33];
     pdl_trigger();
     pdl_wait();
-    const long long wid = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    const int lane = threadIdx.x & 31;
-    if (wid >= (long long)n_tokens * n_groups) return;
-    const long long t = wid / n_groups;
-    const int grp = (int)(wid % n_groups);
+    const long long t = blockIdx.x / n_groups;
+    const int grp = blockIdx.x % n_groups;
     const int inner = s.H * s.P, per = inner / n_groups;
     const int c0 = grp * per;
     auto gated = [&](int c) -> float {
         const float z = ssm_proj(p, s, t, s.z_off + c);
         return y[t * inner + c] * z / (1.0f + expf(-z));
     };
+    float keep[8];
     float ss = 0.f;
-    for (int e = lane; e < per; e += 32) { const float v = gated(c0 + e); ss += v * v; }
-    ss = warp_sum(ss);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = threadIdx.x + i * blockDim.x;
+        keep[i] = e < per ? gated(c0 + e) : 0.f;
+        ss += keep[i] * keep[i];
+    }
+    for (int e = threadIdx.x + 8 * blockDim.x; e < per; e += blockDim.x) { const float v = gated(c0 + e); ss += v * v; }
+    ss = block_sum(ss, red);
     const float inv = inv_rms(ss, (float)per, eps) * scale;
-    for (int e = lane; e < per; e += 32) out[t * inner + c0 + e] = from_f32<TO>(gated(c0 + e) * inv * w[c0 + e]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const int e = threadIdx.x + i * blockDim.x;
+        if (e < per) out[t * inner + c0 + e] = from_f32<TO>(keep[i] * inv * w[c0 + e]);
+    }
+    for (int e = threadIdx.x + 8 * blockDim.x; e < per; e += blockDim.x)
+        out[t * inner + c0 + e] = from_f32<TO>(gated(c0 + e) * inv * w[c0 + e]);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -287,13 +300,17 @@ UB_API int ub_ssm_scan(const float* xbc, const float* dtv, const float* dec, con
                        const int* seq_start, const int* seq_slot, int n_seqs, int H, int P, int N, int G, cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || P <= 0 || N <= 0 || N > 256 || H > 65535 || n_seqs > 65535) return UB_ERR_ARG;
-    const dim3 grid((P + 15) / 16, H, n_seqs), block(128);
-    const int per = (N + 7) / 8;
+    const int lanes = N >= 128 ? 32 : (N >= 64 ? 16 : 8);
+    const int cols = 256 / lanes;
+    const dim3 grid((P + cols - 1) / cols, H, n_seqs), block(256);
+    const int per = (N + lanes - 1) / lanes;               // at most 8: N <= 256
     const bool vec = N % 4 == 0 && P % 4 == 0 && (((uintptr_t)xbc) & 15) == 0;
     cudaError_t e;
-#define GO(RR) e = vec ? ub_launch_dependent(ssm_scan_kernel<RR, true>, grid, block, 0, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G) \
-                       : ub_launch_dependent(ssm_scan_kernel<RR, false>, grid, block, 0, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G)
-    if (per <= 4) GO(4); else if (per <= 8) GO(8); else if (per <= 16) GO(16); else GO(32);
+#define GO2(RR, LL) e = vec ? ub_launch_dependent(ssm_scan_kernel<RR, LL, true>, grid, block, 0, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G) \
+                            : ub_launch_dependent(ssm_scan_kernel<RR, LL, false>, grid, block, 0, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G)
+#define GO(RR) do { if (lanes == 32) GO2(RR, 32); else if (lanes == 16) GO2(RR, 16); else GO2(RR, 8); } while (0)
+    if (per <= 4) GO(4); else GO(8);
+#undef GO2
 #undef GO
     return (int)e;
 }
@@ -305,8 +322,9 @@ UB_API int ub_ssm_finish(const float* y, const float* p, long long ldp, int n_pa
     SsmShape s;
     if (int rc = read_shape(shape, ldp, n_parts, part_stride, s)) return rc;
     if (n_groups < 1 || (s.H * s.P) % n_groups) return UB_ERR_ARG;
-    const long long warps = (long long)n_tokens * n_groups;
-    const unsigned grid = (unsigned)((warps + 3) / 4);
+    const long long blocks = (long long)n_tokens * n_groups;
+    if (blocks > 0x7fffffffLL) return UB_ERR_ARG;
+    const unsigned grid = (unsigned)blocks;
     cudaError_t e;
     if (out_dtype == UB_F32)
         e = ub_launch_dependent(ssm_finish_kernel<float>, dim3(grid), dim3(128), 0, st, y, p, s, w, (float*)out, n_tokens, n_groups, eps, scale);
