@@ -307,8 +307,14 @@ def test_tensor_core_attention_with_the_further_options_prompts_and_single_token
     if cfg["slope"] is not None:
         sl = 2.0 ** (-cfg["slope"] * torch.arange(1, nh + 1, dtype=torch.float64) / nh)
         slopes, sl2 = sl.float(), (sl * np.log2(np.e)).float().to(DEV)
-    for befores, news, slices in (([0, 0, 0, 0], [1, 17, 64, 200], None), ([5, 64, 130, 0], [70, 1, 33, 129], None),
-                                  ([299, 0, 63, 130], [1, 1, 1, 1], 1), ([299, 150, 64, 7], [1, 1, 1, 1], 4)):
+    # (head sizes 64 and 128 without window and bias: the prompts run on the tcgen05 kernels, 128 rows a CTA; the
+    # last case, a long prompt, on the one with 256 rows)
+    cases = [([0, 0, 0, 0], [1, 17, 64, 200], None, 0), ([5, 64, 130, 0], [70, 1, 33, 129], None, 0),
+             ([299, 0, 63, 130], [1, 1, 1, 1], 1, 0), ([299, 150, 64, 7], [1, 1, 1, 1], 4, 0)]
+    if hd in (64, 128) and not cfg["window"] and cfg["slope"] is None:
+        cases += [([0, 20], [320, 300], None, 2), ([5, 64, 130, 0], [70, 1, 33, 129], None, 2)]      # 256 rows a CTA
+    for befores, news, slices, wide in cases:
+        attn_tc.set_wide(wide)
         lens = [b + n for b, n in zip(befores, news)]
         g = torch.Generator().manual_seed(hd + len(lens) + befores[0])
         pages = 5
@@ -349,6 +355,7 @@ def test_tensor_core_attention_with_the_further_options_prompts_and_single_token
                 assert torch.isfinite(got).all(), (cfg, s_, t)
                 err = rel_err(got, ref)
                 assert err <= 2 ** -6, (cfg, befores, news, s_, t, err)
+    attn_tc.set_wide(1)
 
 
 def test_the_sink_takes_weight_when_no_key_fits():

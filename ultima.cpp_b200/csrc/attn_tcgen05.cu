@@ -56,7 +56,30 @@ struct TcAttnParams {
     // decode (one new token a sequence, keys in slices): unnormalised partial results
     float* part_o; float* part_ml; int n_slices, nh;
     int n_seqs, n_row_tiles;                  // prompts: the grid is n_row_tiles * n_seqs * nkv blocks
+    // prompts only: a sink in the softmax's sum (one more term exp(0) that brings no value), a constant on the
+    // output, and one gate an output element (float32 [tokens, heads * HD], row stride g_stride) whose sigmoid
+    // multiplies the output
+    int sink; float out_scale; const float* gate; long long g_stride;
 };
+
+// eight neighbouring outputs of a row, scaled, gated (g: the row's gate values at these columns, or null), packed
+__device__ __forceinline__ uint4 pack_out8(const uint32_t* oo, float inv, const float* __restrict__ g) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(oo[i]) * inv;
+    if (g) {
+        const float4 g0 = *reinterpret_cast<const float4*>(g), g1 = *reinterpret_cast<const float4*>(g + 4);
+        const float gv[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= 1.0f / (1.0f + __expf(-gv[i]));
+    }
+    uint4 w;
+    __nv_bfloat162 a0 = __floats2bfloat162_rn(v[0], v[1]), a1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 a2 = __floats2bfloat162_rn(v[4], v[5]), a3 = __floats2bfloat162_rn(v[6], v[7]);
+    w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
+    w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
+    return w;
+}
 
 __host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, int b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
@@ -286,6 +309,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         const int st = (warp - 2) * 32 + lane;             // 0..127 among the softmax threads
         float m_ref = -INFINITY, l = 0.f;
+        if (!DECODE && p.sink) { m_ref = 0.f; l = 1.f; }    // the sink: a key with score 0 and no value
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
             const int b = j & 1;
@@ -379,9 +403,10 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         if (ok) {
             tc_fence_after();
             const bool partial = DECODE && p.n_slices > 1;
-            const float inv = partial ? 1.0f : (l > 0.f ? 1.0f / l : 0.f);
+            const float inv = partial ? 1.0f : (l > 0.f ? p.out_scale / l : 0.f);
             const int head = kvh * G + g;
             bf16* dst = p.out + (long long)(q0 + tok) * p.o_stride + (long long)head * HD;
+            const float* gt = (!DECODE && p.gate && row_ok) ? p.gate + (long long)(q0 + tok) * p.g_stride + (long long)head * HD : nullptr;
             const long long pi = partial ? ((long long)seq * p.nh + head) * p.n_slices + blockIdx.x : 0;
             if (partial && row_ok) { p.part_ml[pi * 2] = m_ref; p.part_ml[pi * 2 + 1] = l; }
 #pragma unroll
@@ -400,16 +425,8 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                         *reinterpret_cast<uint4*>(p.part_o + pi * HD + cb * 32 + i) = make_uint4(oo[i], oo[i + 1], oo[i + 2], oo[i + 3]);
                 } else if (row_ok) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 8) {
-                        uint4 w;
-                        __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(oo[i]) * inv, __uint_as_float(oo[i + 1]) * inv);
-                        __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(oo[i + 2]) * inv, __uint_as_float(oo[i + 3]) * inv);
-                        __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(oo[i + 4]) * inv, __uint_as_float(oo[i + 5]) * inv);
-                        __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(oo[i + 6]) * inv, __uint_as_float(oo[i + 7]) * inv);
-                        w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
-                        w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
-                        *reinterpret_cast<uint4*>(dst + cb * 32 + i) = w;
-                    }
+                    for (int i = 0; i < 32; i += 8)
+                        *reinterpret_cast<uint4*>(dst + cb * 32 + i) = pack_out8(oo + i, inv, gt ? gt + cb * 32 + i : nullptr);
                 }
             }
         }
@@ -649,6 +666,7 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         uint64_t* pd = pv_done + 2 * t;
         const int st = (warp & 3) * 32 + lane;             // 0..127 among the tile's softmax threads
         float m_ref = -INFINITY, l = 0.f;
+        if (p.sink) { m_ref = 0.f; l = 1.f; }               // the sink: a key with score 0 and no value
         bool ok = true;
         for (int i = 0; i < n_act && ok; ++i) {
             const int b = i & 1;
@@ -740,9 +758,10 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
         if (ok && n_act > 0) ok = mbar_wait(&pd[(n_act - 1) & 1], (uint32_t)(((n_act - 1) >> 1) & 1), err);
         if (ok && n_act > 0) {
             tc_fence_after();
-            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            const float inv = l > 0.f ? p.out_scale / l : 0.f;
             const int head = kvh * G + g;
             bf16* dst = p.out + (long long)(q0 + tok) * p.o_stride + (long long)head * HD;
+            const float* gt = (p.gate && row_ok) ? p.gate + (long long)(q0 + tok) * p.g_stride + (long long)head * HD : nullptr;
 #pragma unroll
             for (int cb = 0; cb < HD / 32; ++cb) {
                 uint32_t oo[32];
@@ -750,16 +769,8 @@ attn_tc_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_cons
                 tmem_ld_wait();
                 if (row_ok) {
 #pragma unroll
-                    for (int x = 0; x < 32; x += 8) {
-                        uint4 w;
-                        __nv_bfloat162 a0 = __floats2bfloat162_rn(__uint_as_float(oo[x]) * inv, __uint_as_float(oo[x + 1]) * inv);
-                        __nv_bfloat162 a1 = __floats2bfloat162_rn(__uint_as_float(oo[x + 2]) * inv, __uint_as_float(oo[x + 3]) * inv);
-                        __nv_bfloat162 a2 = __floats2bfloat162_rn(__uint_as_float(oo[x + 4]) * inv, __uint_as_float(oo[x + 5]) * inv);
-                        __nv_bfloat162 a3 = __floats2bfloat162_rn(__uint_as_float(oo[x + 6]) * inv, __uint_as_float(oo[x + 7]) * inv);
-                        w.x = *reinterpret_cast<uint32_t*>(&a0); w.y = *reinterpret_cast<uint32_t*>(&a1);
-                        w.z = *reinterpret_cast<uint32_t*>(&a2); w.w = *reinterpret_cast<uint32_t*>(&a3);
-                        *reinterpret_cast<uint4*>(dst + cb * 32 + x) = w;
-                    }
+                    for (int x = 0; x < 32; x += 8)
+                        *reinterpret_cast<uint4*>(dst + cb * 32 + x) = pack_out8(oo + x, inv, gt ? gt + cb * 32 + x : nullptr);
                 }
             }
         }
@@ -855,10 +866,35 @@ static int launch_wide(unsigned blocks, const void* map_q, const void* map_k, co
 
 // mode 0: prompts (any numbers of new tokens); mode 1: one new token a sequence, keys in n_slices slices
 // (part_o: float32 [n_seqs, nh, n_slices, HD], part_ml: [.., 2] when n_slices > 1).
+static int attn_tc_launch(int mode, const void* map_q, const void* map_k, const void* map_v, void* out, long long o_stride,
+                          const int* seq_start, const int* seq_before, const int* table, int pages_per_seq,
+                          int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window, float scale,
+                          int n_slices, float* part_o, float* part_ml, int* error, int sink, float out_scale,
+                          const float* gate, long long g_stride, cudaStream_t st);
+
 UB_API int ub_attn_tc(int mode, const void* map_q, const void* map_k, const void* map_v, void* out, long long o_stride,
                       const int* seq_start, const int* seq_before, const int* table, int pages_per_seq,
                       int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window, float scale,
                       int n_slices, float* part_o, float* part_ml, int* error, cudaStream_t st) {
+    return attn_tc_launch(mode, map_q, map_k, map_v, out, o_stride, seq_start, seq_before, table, pages_per_seq, ring, page, n_seqs,
+                          max_new, nh, nkv, window, scale, n_slices, part_o, part_ml, error, 0, 1.0f, nullptr, 0, st);
+}
+
+// Prompts with a sink in the softmax's sum, a constant on the output and a gate an output element (see TcAttnParams).
+UB_API int ub_attn_tc_ext(const void* map_q, const void* map_k, const void* map_v, void* out, long long o_stride,
+                          const int* seq_start, const int* seq_before, const int* table, int pages_per_seq,
+                          int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window, float scale, int* error,
+                          int sink, float out_scale, const float* gate, long long g_stride, cudaStream_t st) {
+    if (gate && (((uintptr_t)gate & 15) || (g_stride % 4) != 0)) return UB_ERR_ARG;
+    return attn_tc_launch(0, map_q, map_k, map_v, out, o_stride, seq_start, seq_before, table, pages_per_seq, ring, page, n_seqs,
+                          max_new, nh, nkv, window, scale, 1, nullptr, nullptr, error, sink, out_scale, gate, g_stride, st);
+}
+
+static int attn_tc_launch(int mode, const void* map_q, const void* map_k, const void* map_v, void* out, long long o_stride,
+                          const int* seq_start, const int* seq_before, const int* table, int pages_per_seq,
+                          int ring, int page, int n_seqs, int max_new, int nh, int nkv, int window, float scale,
+                          int n_slices, float* part_o, float* part_ml, int* error, int sink, float out_scale,
+                          const float* gate, long long g_stride, cudaStream_t st) {
     if (n_seqs <= 0 || max_new <= 0) return 0;
     const int group = nh / nkv;
     if (page != BN || ring % page != 0 || nh % nkv != 0 || group > BM || (o_stride % 8) != 0 || ((uintptr_t)out & 15))
@@ -870,6 +906,8 @@ UB_API int ub_attn_tc(int mode, const void* map_q, const void* map_k, const void
     p.c = scale * 1.4426950408889634f; p.error = error;
     p.part_o = part_o; p.part_ml = part_ml; p.n_slices = n_slices < 1 ? 1 : n_slices; p.nh = nh;
     p.n_seqs = n_seqs; p.n_row_tiles = 1;
+    p.sink = sink ? 1 : 0; p.out_scale = out_scale; p.gate = gate; p.g_stride = g_stride;
+    if (mode != 0 && (sink || gate || out_scale != 1.0f)) return UB_ERR_ARG;
     if (mode == 0) {
         p.n_slices = 1;
         const int tpb = BM / group;

@@ -107,6 +107,16 @@ __device__ __forceinline__ void ssm_cp16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
 }
 
+// Stages of tokens in shared memory: SSM_STAGES - 1 of them are on their way while one is worked on (a copy from
+// the L2 takes about as long as the arithmetic of several dozen tokens).
+constexpr int SSM_STAGES = 4;
+template <int R, int LANES>
+struct SsmScanLayout {
+    static constexpr int NP = LANES * R, COLS = 256 / LANES;
+    static constexpr int TT = NP <= 128 ? 16 : 8;         // tokens a stage
+    static constexpr size_t BYTES = (size_t)SSM_STAGES * TT * (2 * NP + COLS + 2) * sizeof(float);
+};
+
 // VEC: N, P and the row stride are multiples of 4 and xbc starts on a 16-byte boundary: 16-byte copies.
 template <int R, int LANES, bool VEC>
 __global__ void __launch_bounds__(256)
@@ -115,10 +125,13 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
                 const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int H, int P, int N, int G) {
     static_assert(R % 4 == 0, "a lane holds whole float4 chunks");
     constexpr int COLS = 256 / LANES, NP = LANES * R, NC = R / 4;
-    constexpr int TT = NP <= 64 ? 16 : 8;                 // tokens a stage
-    __shared__ __align__(16) float sB[2][TT][NP], sC[2][TT][NP];
-    __shared__ __align__(16) float sx[2][TT][COLS];
-    __shared__ float sdt[2][TT], sa[2][TT];
+    constexpr int TT = SsmScanLayout<R, LANES>::TT, ST = SSM_STAGES;
+    extern __shared__ __align__(16) float smem[];
+    float (*sB)[TT][NP] = reinterpret_cast<float (*)[TT][NP]>(smem);                       // [ST][TT][NP]
+    float (*sC)[TT][NP] = reinterpret_cast<float (*)[TT][NP]>(smem + ST * TT * NP);
+    float (*sx)[TT][COLS] = reinterpret_cast<float (*)[TT][COLS]>(smem + 2 * ST * TT * NP);
+    float (*sdt)[TT] = reinterpret_cast<float (*)[TT]>(smem + 2 * ST * TT * NP + ST * TT * COLS);
+    float (*sa)[TT] = reinterpret_cast<float (*)[TT]>(smem + 2 * ST * TT * NP + ST * TT * COLS + ST * TT);
     pdl_trigger();
     pdl_wait();
     const int tid = threadIdx.x, col = tid / LANES, l = tid % LANES;
@@ -135,54 +148,54 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
         s[i] = (n < N && j < P) ? Sh[(long long)n * P + j] : 0.f;
     }
     // channels past the sizes are zeros that no copy ever touches
-    for (int idx = tid; idx < 2 * TT * NP; idx += blockDim.x)
+    for (int idx = tid; idx < ST * TT * NP; idx += blockDim.x)
         if (idx % NP >= N) { (&sB[0][0][0])[idx] = 0.f; (&sC[0][0][0])[idx] = 0.f; }
-    for (int idx = tid; idx < 2 * TT * COLS; idx += blockDim.x)
+    for (int idx = tid; idx < ST * TT * COLS; idx += blockDim.x)
         if (blockIdx.x * COLS + idx % COLS >= P) (&sx[0][0][0])[idx] = 0.f;
     const float dh = Dw[h];
     const float* brow = xbc + H * P + g * N;
     const float* xrow = xbc + h * P + blockIdx.x * COLS;
+    // one group of copies is committed for every stage, empty past the end, so the count to wait for is fixed
     auto fetch = [&](int base, int buf) {
         const int cnt = min(TT, t1 - base);
-        if (VEC) {
-            const int n4 = N >> 2;
-            for (int idx = tid; idx < cnt * n4; idx += blockDim.x) {
-                const int tt = idx / n4, n = (idx % n4) * 4;
-                const float* rowp = brow + (long long)(base + tt) * C;
-                ssm_cp16(&sB[buf][tt][n], rowp + n);
-                ssm_cp16(&sC[buf][tt][n], rowp + G * N + n);
+        if (cnt > 0) {
+            if (VEC) {
+                const int n4 = N >> 2;
+                for (int idx = tid; idx < cnt * n4; idx += blockDim.x) {
+                    const int tt = idx / n4, n = (idx % n4) * 4;
+                    const float* rowp = brow + (long long)(base + tt) * C;
+                    ssm_cp16(&sB[buf][tt][n], rowp + n);
+                    ssm_cp16(&sC[buf][tt][n], rowp + G * N + n);
+                }
+                if (tid < cnt * (COLS / 4)) {
+                    const int tt = tid / (COLS / 4), cc = (tid % (COLS / 4)) * 4;
+                    if (blockIdx.x * COLS + cc < P) ssm_cp16(&sx[buf][tt][cc], xrow + (long long)(base + tt) * C + cc);
+                }
+            } else {
+                for (int idx = tid; idx < cnt * N; idx += blockDim.x) {
+                    const int tt = idx / N, n = idx % N;
+                    const float* rowp = brow + (long long)(base + tt) * C;
+                    ssm_cp4(&sB[buf][tt][n], rowp + n);
+                    ssm_cp4(&sC[buf][tt][n], rowp + G * N + n);
+                }
+                for (int idx = tid; idx < cnt * COLS; idx += blockDim.x) {
+                    const int tt = idx / COLS, cc = idx % COLS;
+                    if (blockIdx.x * COLS + cc < P) ssm_cp4(&sx[buf][tt][cc], xrow + (long long)(base + tt) * C + cc);
+                }
             }
-            if (tid < cnt * (COLS / 4)) {
-                const int tt = tid / (COLS / 4), cc = (tid % (COLS / 4)) * 4;
-                if (blockIdx.x * COLS + cc < P) ssm_cp16(&sx[buf][tt][cc], xrow + (long long)(base + tt) * C + cc);
-            }
-        } else {
-            for (int idx = tid; idx < cnt * N; idx += blockDim.x) {
-                const int tt = idx / N, n = idx % N;
-                const float* rowp = brow + (long long)(base + tt) * C;
-                ssm_cp4(&sB[buf][tt][n], rowp + n);
-                ssm_cp4(&sC[buf][tt][n], rowp + G * N + n);
-            }
-            for (int idx = tid; idx < cnt * COLS; idx += blockDim.x) {
-                const int tt = idx / COLS, cc = idx % COLS;
-                if (blockIdx.x * COLS + cc < P) ssm_cp4(&sx[buf][tt][cc], xrow + (long long)(base + tt) * C + cc);
-            }
+            if (tid >= 128 && tid < 128 + cnt) ssm_cp4(&sdt[buf][tid - 128], dtv + (long long)(base + tid - 128) * H + h);
+            if (tid >= 192 && tid < 192 + cnt) ssm_cp4(&sa[buf][tid - 192], dec + (long long)(base + tid - 192) * H + h);
         }
-        if (tid >= 64 && tid < 64 + cnt) ssm_cp4(&sdt[buf][tid - 64], dtv + (long long)(base + tid - 64) * H + h);
-        if (tid >= 96 && tid < 96 + cnt) ssm_cp4(&sa[buf][tid - 96], dec + (long long)(base + tid - 96) * H + h);
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     __syncthreads();                                       // the constants above are in place before any copy lands beside them
-    fetch(t0, 0);
+#pragma unroll
+    for (int i = 0; i < ST - 1; ++i) fetch(t0 + i * TT, i);
     int buf = 0;
-    for (int base = t0; base < t1; base += TT, buf ^= 1) {
+    for (int base = t0; base < t1; base += TT, buf = (buf + 1) % ST) {
         const int cnt = min(TT, t1 - base);
-        if (base + TT < t1) {
-            fetch(base + TT, buf ^ 1);                     // (that buffer's readers passed the barrier at the end of the last round)
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-        } else {
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-        }
+        fetch(base + (ST - 1) * TT, (buf + ST - 1) % ST);  // (that buffer's readers passed the barrier at the end of the last round)
+        asm volatile("cp.async.wait_group %0;" ::"n"(ST - 1) : "memory");
         __syncthreads();
         auto token = [&](int tt) {
             const float4* B4 = reinterpret_cast<const float4*>(sB[buf][tt]);
@@ -216,6 +229,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
         }
         __syncthreads();                                   // this buffer is asked for again in the next round
     }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < R; ++i) {
         const int n = ((i >> 2) * LANES + l) * 4 + (i & 3);
@@ -306,11 +320,21 @@ UB_API int ub_ssm_scan(const float* xbc, const float* dtv, const float* dec, con
     const int per = (N + lanes - 1) / lanes;               // at most 8: N <= 256
     const bool vec = N % 4 == 0 && P % 4 == 0 && (((uintptr_t)xbc) & 15) == 0;
     cudaError_t e;
-#define GO2(RR, LL) e = vec ? ub_launch_dependent(ssm_scan_kernel<RR, LL, true>, grid, block, 0, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G) \
-                            : ub_launch_dependent(ssm_scan_kernel<RR, LL, false>, grid, block, 0, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G)
+#define GO3(RR, LL, VV) do { \
+        constexpr size_t smem = SsmScanLayout<RR, LL>::BYTES; \
+        static bool attr_done = false; \
+        if (!attr_done) { \
+            e = cudaFuncSetAttribute(ssm_scan_kernel<RR, LL, VV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) return (int)e; \
+            attr_done = true; \
+        } \
+        e = ub_launch_dependent(ssm_scan_kernel<RR, LL, VV>, grid, block, smem, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G); \
+    } while (0)
+#define GO2(RR, LL) do { if (vec) GO3(RR, LL, true); else GO3(RR, LL, false); } while (0)
 #define GO(RR) do { if (lanes == 32) GO2(RR, 32); else if (lanes == 16) GO2(RR, 16); else GO2(RR, 8); } while (0)
     if (per <= 4) GO(4); else GO(8);
 #undef GO2
+#undef GO3
 #undef GO
     return (int)e;
 }

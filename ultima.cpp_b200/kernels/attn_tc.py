@@ -77,6 +77,10 @@ def tc_lib(head_dim: int):
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p,
                                  c_void_p, c_void_p, c_void_p]
         L.ub_attn_tc.restype = c_int
+        L.ub_attn_tc_ext.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_void_p, c_void_p,
+                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
+                                     c_int, c_float, c_void_p, c_longlong, c_void_p]
+        L.ub_attn_tc_ext.restype = c_int
         L.ub_attn_tc_set_wide.argtypes = [c_int]
         L.ub_attn_tc_set_wide.restype = None
         L.ub_attn_tc_set_wide(WIDE)
@@ -262,10 +266,29 @@ def attention_ext(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, w
     the attention part: ``window`` with ``keep_first`` positions kept visible behind it, ``sink``, ``slopes_log2``
     (float32 [heads], slope * log2(e)), ``out_scale`` and ``gate`` (float32 [T, heads * head size], contiguous: one
     sigmoid gate an output element).  The cache holds every position or is a ring of the window's size."""
-    L = lib(head_dim)
     assert out.dtype == torch.bfloat16 and out.stride(1) == 1
     group = n_heads // n_kv_heads
     decode = batch.max_new == 1 and group <= 16
+    if gate is not None:
+        assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (q.shape[0], n_heads * head_dim)
+    # prompts without a window and without a bias by distance: the tcgen05 kernels know the sink, the scale and the gate
+    if (not decode and not window and not keep_first and slopes_log2 is None and tcgen05_fits(head_dim, n_heads, n_kv_heads)
+            and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0 and kv.k.is_contiguous() and kv.v.is_contiguous()
+            and (gate is None or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 4 == 0))):
+        L = tc_lib(head_dim)
+        T = q.shape[0]
+        mq = _tc_map(("q", q.data_ptr(), T, n_heads, q.stride(0), group, head_dim),
+                     lambda a: L.ub_attn_tc_map_q(a, q.data_ptr(), T, n_heads, q.stride(0), group))
+        mk = _tc_map(("kv", kv.k.data_ptr(), kv.k.shape[0], n_kv_heads, head_dim),
+                     lambda a: L.ub_attn_tc_map_kv(a, kv.k.data_ptr(), kv.k.shape[0], n_kv_heads))
+        mv = _tc_map(("kv", kv.v.data_ptr(), kv.v.shape[0], n_kv_heads, head_dim),
+                     lambda a: L.ub_attn_tc_map_kv(a, kv.v.data_ptr(), kv.v.shape[0], n_kv_heads))
+        rc = L.ub_attn_tc_ext(mq, mk, mv, _ptr(out), out.stride(0), _ptr(batch.seq_start), _ptr(batch.seq_before),
+                              _ptr(kv.table), kv.table.shape[1], kv.ring, kv.page, batch.n_seqs, batch.max_new, n_heads,
+                              n_kv_heads, 0, float(scale), _ptr(rt.status[1:2]), 1 if sink else 0, float(out_scale),
+                              _ptr(gate), gate.stride(0) if gate is not None else 0, _stream())
+        return _check(rc, "attn_tc_ext")
+    L = lib(head_dim)
     part_o = part_ml = None
     n_slices = 1
     if decode:
@@ -274,8 +297,6 @@ def attention_ext(q, kv, out, batch, n_heads, n_kv_heads, head_dim, scale, rt, w
         if n_slices > 1:
             part_o = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, head_dim), torch.float32)
             part_ml = rt.arena.alloc((batch.n_seqs, n_heads, n_slices, 2), torch.float32)
-    if gate is not None:
-        assert gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (q.shape[0], n_heads * head_dim)
     rc = L.ub_attn_mma_ext(1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kv.k), _ptr(kv.v),
                            _ptr(batch.seq_start), _ptr(batch.seq_before), _ptr(kv.table), kv.table.shape[1], kv.ring,
                            kv.page, batch.n_seqs, batch.max_new, n_heads, n_kv_heads, int(window or 0), float(scale),

@@ -124,6 +124,8 @@ class Attention(Mixer):
             if self.extended:
                 if self._fast_extended() and attn_tc.EXTENDED:
                     out.append(attn_tc.target(self.hd))
+                    if self.hd in catalog.TC_HEAD_DIMS and not self.window and self.distance_slope is None:
+                        out.append(attn_tc.tc_target(self.hd))
                 return out
             if self._fast_attention() and attn_tc.BLOCK_MASK:
                 out.append(attn_tc.target(self.hd))
