@@ -147,6 +147,28 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
         const int n = ((i >> 2) * LANES + l) * 4 + (i & 3);
         s[i] = (n < N && j < P) ? Sh[(long long)n * P + j] : 0.f;
     }
+    if (t1 - t0 == 1) {
+        // one token (a decode step): straight from global memory, no stages
+        const float* rowp = xbc + (long long)t0 * C;
+        const float a = dec[(long long)t0 * H + h];
+        const float xv = j < P ? rowp[h * P + j] : 0.f;
+        const float u = dtv[(long long)t0 * H + h] * xv;
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int n = ((i >> 2) * LANES + l) * 4 + (i & 3);
+            const float bv = n < N ? rowp[H * P + g * N + n] : 0.f;
+            const float cv = n < N ? rowp[H * P + G * N + g * N + n] : 0.f;
+            s[i] = fmaf(a, s[i], bv * u);
+            part[i & 3] = fmaf(s[i], cv, part[i & 3]);
+            if (n < N && j < P) Sh[(long long)n * P + j] = s[i];
+        }
+        float sum = (part[0] + part[1]) + (part[2] + part[3]);          // (the order of the stages' sum: chunk by chunk, then the four)
+#pragma unroll
+        for (int w = 1; w < LANES; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
+        if (l == 0 && j < P) y[((long long)t0 * H + h) * P + j] = fmaf(Dw[h], xv, sum);
+        return;
+    }
     // channels past the sizes are zeros that no copy ever touches
     for (int idx = tid; idx < ST * TT * NP; idx += blockDim.x)
         if (idx % NP >= N) { (&sB[0][0][0])[idx] = 0.f; (&sC[0][0][0])[idx] = 0.f; }

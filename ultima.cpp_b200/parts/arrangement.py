@@ -1,11 +1,17 @@
 """How a layer's parts are arranged around the residual stream."""
 from __future__ import annotations
 
+import os
+
 from ..kernels import ops
 import torch
 
 from ..weights.spec import WeightSpec
 from .base import Arrangement, Entry, ResidualGate, register_part
+
+
+# ULTIMA_FUSE_INPUTS=0: every part of a parallel layer runs its own input product (for measurements)
+FUSE_INPUTS = os.environ.get("ULTIMA_FUSE_INPUTS", "1") != "0"
 
 
 @register_part("arrangement", "pre_norm")
@@ -111,18 +117,11 @@ class SigmoidLinearGate(ResidualGate):
             rt.matmul(h, w, g)
         return g
 
-    @classmethod
-    def fused_sums(cls, gates, h, rt):
-        """One product for all of a layer's gates: their matrices stacked (made once, kept on the first gate)."""
-        if len(gates) < 2 or any(type(g) is not cls or g.w.dtype != gates[0].w.dtype or g.width != gates[0].width for g in gates):
-            return None
-        first = gates[0]
-        if getattr(first, "_stacked_for", None) != tuple(id(g) for g in gates):
-            first._stacked = torch.cat([g.w for g in gates], dim=0).contiguous()
-            first._stacked_for = tuple(id(g) for g in gates)
-        s = cls._sums(h, first._stacked, rt)
-        w = first.width
-        return [s[..., i * w:(i + 1) * w] for i in range(len(gates))]
+    def input_weight(self):
+        return self.w
+
+    def adopt_input_weight(self, w):
+        self.w = w
 
     def join(self, h, y, x, rt, sums=None):
         g = sums if sums is not None else self._sums(h, self.w, rt)
@@ -151,15 +150,47 @@ class _ParallelGated(Arrangement):
         h = layer.norm.forward(x, rt)
         ff = getattr(layer, "feed_forward", None)
         gates = [layer.mixer_gate] + ([layer.feed_forward_gate] if ff is not None else [])
-        sums = type(gates[0]).fused_sums(gates, h, rt) or [None] * len(gates)       # one product for both gates where they can
+        # one product for everything that reads h and takes float32 sums: the mixer's input projections and the gates'
+        sums = self._input_sums(layer, [layer.mixer] + gates, h, rt)
         inner = rt.arena.mark()
-        layer.mixer.forward(h, y, batch, cache, rt)
-        gates[0].join(h, y, x, rt, sums[0])
+        if sums[0] is not None:
+            layer.mixer.forward(h, y, batch, cache, rt, projected=sums[0])
+        else:
+            layer.mixer.forward(h, y, batch, cache, rt)
+        gates[0].join(h, y, x, rt, sums[1])
         rt.arena.reset(inner)
         if ff is not None:
             ff.forward(h, y, batch, rt)
-            gates[1].join(h, y, x, rt, sums[1])
+            gates[1].join(h, y, x, rt, sums[2])
         rt.arena.reset(mark)
+
+    @staticmethod
+    def _input_sums(layer, parts, h, rt):
+        """For each of ``parts`` the float32 sums of h with its ``input_weight`` (None where it has none), from ONE
+        product over the stacked matrices.  The stack is made at the layer's first run; the parts then hold views
+        of it instead of copies of their own."""
+        plan = getattr(layer, "_stacked_inputs", None)
+        if plan is None:
+            ws = [p.input_weight() for p in parts]
+            take = [i for i, w in enumerate(ws) if w is not None]
+            plan = False
+            if FUSE_INPUTS and len(take) > 1 and len({(ws[i].dtype, ws[i].shape[1], ws[i].device) for i in take}) == 1:
+                stacked = torch.cat([ws[i] for i in take], dim=0).contiguous()
+                spans, at = {}, 0
+                for i in take:
+                    spans[i] = (at, at + ws[i].shape[0])
+                    parts[i].adopt_input_weight(stacked[at:at + ws[i].shape[0]])
+                    at += ws[i].shape[0]
+                plan = (stacked, spans)
+            layer._stacked_inputs = plan
+        if not plan:
+            return [None] * len(parts)
+        stacked, spans = plan
+        s = rt.matmul_parts(h, stacked)
+        if s is None:
+            s = rt.arena.alloc((h.shape[0], stacked.shape[0]), torch.float32)
+            rt.matmul(h, stacked, s)
+        return [s[..., spans[i][0]:spans[i][1]] if i in spans else None for i in range(len(parts))]
 
 
 @register_part("arrangement", "parallel_gated")

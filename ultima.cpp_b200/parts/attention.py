@@ -183,7 +183,14 @@ class Attention(Mixer):
             self.slopes = slopes.float().contiguous().to(rt.device)
             self.slopes_log2 = (slopes * math.log2(math.e)).float().contiguous().to(rt.device)   # for kernels that work in powers of two
 
-    def _forward_general(self, h, residual, batch, cache, rt):
+    def input_weight(self):
+        """The stacked [q | k | v | gate] matrix of a layer on the general kernels, which take its float32 sums."""
+        return self.wqkv if self.general else None
+
+    def adopt_input_weight(self, w):
+        self.wqkv = w
+
+    def _forward_general(self, h, residual, batch, cache, rt, projected=None):
         """One product [q | k | v | gate] in float32, placement (norm, rotation, cache write), attention
         with the block mask, the gate, the output projection."""
         T = h.shape[0]
@@ -192,7 +199,7 @@ class Attention(Mixer):
             raise ValueError("attention: a layer without keys and values of its own must read another run's "
                              "cache, and one with them must own its cache")
         rot = self.position.rotation() if self.position is not None else None
-        x = rt.matmul_parts(h, self.wqkv)            # few tokens: K in slices, summed by the placement kernel
+        x = projected if projected is not None else rt.matmul_parts(h, self.wqkv)    # few tokens: K in slices, summed by the placement kernel
         if x is None:
             x = rt.arena.alloc((T, self.wqkv.shape[0]), torch.float32)
             rt.matmul(h, self.wqkv, x)
@@ -230,9 +237,9 @@ class Attention(Mixer):
                             keep_first=self.keep_first, slopes=self.slopes, sink=self.sink, out_scale=self.out_scale)
         rt.matmul(o, self.wo, residual, ops.EPI_ADD)
 
-    def forward(self, h, residual, batch, cache, rt):
+    def forward(self, h, residual, batch, cache, rt, projected=None):
         if self.general:
-            return self._forward_general(h, residual, batch, cache, rt)
+            return self._forward_general(h, residual, batch, cache, rt, projected)
         T = h.shape[0]
         kv = cache.kv
         # A position encoding that describes itself as a rotation of pairs is applied by the kernels

@@ -106,6 +106,17 @@ class Part:
     def scratch_bytes(self, n_tokens: int, rt) -> int:
         return 0
 
+    def input_weight(self):
+        """A matrix [rows, width] (bound, on the device) by which the part multiplies its input and whose float32
+        sums it can take ready-made, or None.  An arrangement whose parts read the same input may stack these
+        matrices, run one product for all of them, and hand each part its columns (a mixer as
+        ``forward(..., projected=...)``, a gate as ``join(..., sums=...)``): [parts, T, rows] or [T, rows], float32,
+        rows of any stride."""
+        return None
+
+    def adopt_input_weight(self, w) -> None:
+        """Take ``w``, a view of the stacked matrix with this part's rows, in place of the part's own copy."""
+
     def kernel_needs(self, run_dtype) -> list:
         """The libraries of csrc/ this part launches, as (source, (defines...)) pairs, beyond the
         ones every model uses; they are compiled together when the engine is built."""
@@ -172,14 +183,8 @@ class ResidualGate(Part):
 
     def join(self, h, y, x, rt, sums=None) -> None:
         """x += gate(h) * y and y cleared; h: the layer's normed input (activations), x, y: float32 [T, width].
-        ``sums``: what ``fused_sums`` made for this gate, if the arrangement called it."""
+        ``sums``: the product of h with the gate's ``input_weight``, if the arrangement made it."""
         raise NotImplementedError
-
-    @classmethod
-    def fused_sums(cls, gates, h, rt):
-        """Gates of one layer that read the same input may make their sums together: a list with one entry a gate
-        (handed back to each ``join`` as ``sums``), or None if these gates cannot."""
-        return None
 
 
 class Entry(Part):

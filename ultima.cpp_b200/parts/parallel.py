@@ -45,6 +45,19 @@ class SideBySide(Mixer):
         for side, m in (("left.", self.left), ("right.", self.right)):
             m.bind({n[len(side):]: t for n, t in tensors.items() if n.startswith(side)}, rt)
 
+    def input_weight(self):
+        """Both sides' input matrices stacked, if both have one."""
+        import torch
+        a, b = self.left.input_weight(), self.right.input_weight()
+        if a is None or b is None or a.dtype != b.dtype or a.shape[1] != b.shape[1]:
+            return None
+        return torch.cat([a, b], dim=0)
+
+    def adopt_input_weight(self, w):
+        n = self.left.input_weight().shape[0]
+        self.left.adopt_input_weight(w[:n])
+        self.right.adopt_input_weight(w[n:])
+
     def _share(self, cache, which: int):
         """The part of the run's cache that belongs to one side."""
         if cache is None:
@@ -55,9 +68,15 @@ class SideBySide(Mixer):
         kv = cache.kv if any(isinstance(n, KVNeed) for n in self._needs[which]) else None
         return type(cache)(kv=kv, state=states[0] if states else None, owner=cache.owner, states=states)
 
-    def forward(self, h, residual, batch, cache, rt):
+    def forward(self, h, residual, batch, cache, rt, projected=None):
         mark = rt.arena.mark()
-        self.left.forward(h, residual, batch, self._share(cache, 0), rt)
-        rt.arena.reset(mark)
-        self.right.forward(h, residual, batch, self._share(cache, 1), rt)
+        if projected is not None:
+            n = self.left.input_weight().shape[0]
+            self.left.forward(h, residual, batch, self._share(cache, 0), rt, projected=projected[..., :n])
+            rt.arena.reset(mark)
+            self.right.forward(h, residual, batch, self._share(cache, 1), rt, projected=projected[..., n:])
+        else:
+            self.left.forward(h, residual, batch, self._share(cache, 0), rt)
+            rt.arena.reset(mark)
+            self.right.forward(h, residual, batch, self._share(cache, 1), rt)
         rt.arena.reset(mark)

@@ -78,11 +78,17 @@ class StateSpaceDual(Mixer):
         self.shape = ops.ssm_shape(self.nh, self.hd, self.n_state, self.ng, self.conv,
                                    (0, x_off, b_off, c_off, c_off + self.ng * self.n_state))
 
-    def forward(self, h, residual, batch, cache, rt):
+    def input_weight(self):
+        return self.w_in
+
+    def adopt_input_weight(self, w):
+        self.w_in = w
+
+    def forward(self, h, residual, batch, cache, rt, projected=None):
         T = h.shape[0]
         S, conv_state = cache.states
         f32 = torch.float32
-        p = rt.matmul_parts(h, self.w_in)
+        p = projected if projected is not None else rt.matmul_parts(h, self.w_in)
         if p is None:
             p = rt.arena.alloc((T, self.rows), f32)
             rt.matmul(h, self.w_in, p)
