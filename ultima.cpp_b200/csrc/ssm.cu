@@ -91,11 +91,12 @@ __global__ void ssm_conv_state_update_kernel(const float* __restrict__ p, SsmSha
     for (int k = 0; k < K; ++k) st[(long long)k * C + c] = tmp[k];
 }
 
-// The recurrence.  A block of 256 threads takes 256 / LANES value channels of one head of one sequence; LANES
+// The recurrence.  A block of 256 threads takes 256 / LANES * SSM_CPT value channels of one head of one sequence; LANES
 // (8, 16 or 32, by the state's size alone, so that the order of every sum is the same whatever the batch) lanes
 // hold one column of S, lane l the state channels of the float4 chunks l, l + LANES, ...: the lanes of a column
 // read consecutive bytes of shared memory in one instruction.  More lanes a column mean more warps with fewer
-// values each: the kernel is bound by the latency of a token's chain, which many warps hide.  Tokens come through shared memory a stage at a time,
+// values each: the kernel is bound by the latency of a token's chain, which many warps hide.  A thread holds
+// SSM_CPT neighbouring columns, which share its reads of B and C (the kernel issues fewer instructions an element).  Tokens come through shared memory a stage at a time,
 // the next stage asked for (cp.async) while this one is worked on.  The state's update does not wait for the
 // read-out: a token costs two operations a state element and three exchanges.
 __device__ __forceinline__ void ssm_cp4(float* dst, const float* src) {
@@ -110,9 +111,10 @@ __device__ __forceinline__ void ssm_cp16(float* dst, const float* src) {
 // Stages of tokens in shared memory: SSM_STAGES - 1 of them are on their way while one is worked on (a copy from
 // the L2 takes about as long as the arithmetic of several dozen tokens).
 constexpr int SSM_STAGES = 4;
+constexpr int SSM_CPT = 2;                                // columns of S a thread holds: they share every read of B and C
 template <int R, int LANES>
 struct SsmScanLayout {
-    static constexpr int NP = LANES * R, COLS = 256 / LANES;
+    static constexpr int NP = LANES * R, COLS = 256 / LANES * SSM_CPT;
     static constexpr int TT = NP <= 128 ? 16 : 8;         // tokens a stage
     static constexpr size_t BYTES = (size_t)SSM_STAGES * TT * (2 * NP + COLS + 2) * sizeof(float);
 };
@@ -124,7 +126,7 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
                 const float* __restrict__ Dw, float* __restrict__ y, float* __restrict__ S,
                 const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int H, int P, int N, int G) {
     static_assert(R % 4 == 0, "a lane holds whole float4 chunks");
-    constexpr int COLS = 256 / LANES, NP = LANES * R, NC = R / 4;
+    constexpr int CPT = SSM_CPT, COLS = 256 / LANES * CPT, NP = LANES * R, NC = R / 4;
     constexpr int TT = SsmScanLayout<R, LANES>::TT, ST = SSM_STAGES;
     extern __shared__ __align__(16) float smem[];
     float (*sB)[TT][NP] = reinterpret_cast<float (*)[TT][NP]>(smem);                       // [ST][TT][NP]
@@ -134,39 +136,53 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
     float (*sa)[TT] = reinterpret_cast<float (*)[TT]>(smem + 2 * ST * TT * NP + ST * TT * COLS + ST * TT);
     pdl_trigger();
     pdl_wait();
-    const int tid = threadIdx.x, col = tid / LANES, l = tid % LANES;
+    const int tid = threadIdx.x, col = (tid / LANES) * CPT, l = tid % LANES;      // col: the first of this thread's columns
     const int h = blockIdx.y, b = blockIdx.z, g = h / (H / G);
     const int j = blockIdx.x * COLS + col;
     const int t0 = seq_start[b], t1 = seq_start[b + 1];
     if (t0 >= t1) return;
     const int C = H * P + 2 * G * N;
     float* Sh = S + ((long long)seq_slot[b] * H + h) * N * P;
-    float s[R];
+    float s[CPT][R];
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-        const int n = ((i >> 2) * LANES + l) * 4 + (i & 3);
-        s[i] = (n < N && j < P) ? Sh[(long long)n * P + j] : 0.f;
-    }
+    for (int c = 0; c < CPT; ++c)
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int n = ((i >> 2) * LANES + l) * 4 + (i & 3);
+            s[c][i] = (n < N && j + c < P) ? Sh[(long long)n * P + j + c] : 0.f;
+        }
+    const float dh = Dw[h];
     if (t1 - t0 == 1) {
         // one token (a decode step): straight from global memory, no stages
         const float* rowp = xbc + (long long)t0 * C;
         const float a = dec[(long long)t0 * H + h];
-        const float xv = j < P ? rowp[h * P + j] : 0.f;
-        const float u = dtv[(long long)t0 * H + h] * xv;
-        float part[4] = {0.f, 0.f, 0.f, 0.f};
+        const float dt = dtv[(long long)t0 * H + h];
+        float xv[CPT], u[CPT], part[CPT][4];
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            xv[c] = j + c < P ? rowp[h * P + j + c] : 0.f;
+            u[c] = dt * xv[c];
+            part[c][0] = part[c][1] = part[c][2] = part[c][3] = 0.f;
+        }
 #pragma unroll
         for (int i = 0; i < R; ++i) {
             const int n = ((i >> 2) * LANES + l) * 4 + (i & 3);
             const float bv = n < N ? rowp[H * P + g * N + n] : 0.f;
             const float cv = n < N ? rowp[H * P + G * N + g * N + n] : 0.f;
-            s[i] = fmaf(a, s[i], bv * u);
-            part[i & 3] = fmaf(s[i], cv, part[i & 3]);
-            if (n < N && j < P) Sh[(long long)n * P + j] = s[i];
-        }
-        float sum = (part[0] + part[1]) + (part[2] + part[3]);          // (the order of the stages' sum: chunk by chunk, then the four)
 #pragma unroll
-        for (int w = 1; w < LANES; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
-        if (l == 0 && j < P) y[((long long)t0 * H + h) * P + j] = fmaf(Dw[h], xv, sum);
+            for (int c = 0; c < CPT; ++c) {
+                s[c][i] = fmaf(a, s[c][i], bv * u[c]);
+                part[c][i & 3] = fmaf(s[c][i], cv, part[c][i & 3]);
+                if (n < N && j + c < P) Sh[(long long)n * P + j + c] = s[c][i];
+            }
+        }
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            float sum = (part[c][0] + part[c][1]) + (part[c][2] + part[c][3]);   // (the order of the stages' sum: chunk by chunk, then the four)
+#pragma unroll
+            for (int w = 1; w < LANES; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
+            if (l == 0 && j + c < P) y[((long long)t0 * H + h) * P + j + c] = fmaf(dh, xv[c], sum);
+        }
         return;
     }
     // channels past the sizes are zeros that no copy ever touches
@@ -174,7 +190,6 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
         if (idx % NP >= N) { (&sB[0][0][0])[idx] = 0.f; (&sC[0][0][0])[idx] = 0.f; }
     for (int idx = tid; idx < ST * TT * COLS; idx += blockDim.x)
         if (blockIdx.x * COLS + idx % COLS >= P) (&sx[0][0][0])[idx] = 0.f;
-    const float dh = Dw[h];
     const float* brow = xbc + H * P + g * N;
     const float* xrow = xbc + h * P + blockIdx.x * COLS;
     // one group of copies is committed for every stage, empty past the end, so the count to wait for is fixed
@@ -189,8 +204,8 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
                     ssm_cp16(&sB[buf][tt][n], rowp + n);
                     ssm_cp16(&sC[buf][tt][n], rowp + G * N + n);
                 }
-                if (tid < cnt * (COLS / 4)) {
-                    const int tt = tid / (COLS / 4), cc = (tid % (COLS / 4)) * 4;
+                for (int idx = tid; idx < cnt * (COLS / 4); idx += blockDim.x) {
+                    const int tt = idx / (COLS / 4), cc = (idx % (COLS / 4)) * 4;
                     if (blockIdx.x * COLS + cc < P) ssm_cp16(&sx[buf][tt][cc], xrow + (long long)(base + tt) * C + cc);
                 }
             } else {
@@ -214,6 +229,8 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
 #pragma unroll
     for (int i = 0; i < ST - 1; ++i) fetch(t0 + i * TT, i);
     int buf = 0;
+    float* yp = y + ((long long)t0 * H + h) * P + j;       // this thread's place in a token's output row
+    const long long ystep = (long long)H * P;
     for (int base = t0; base < t1; base += TT, buf = (buf + 1) % ST) {
         const int cnt = min(TT, t1 - base);
         fetch(base + (ST - 1) * TT, (buf + ST - 1) % ST);  // (that buffer's readers passed the barrier at the end of the last round)
@@ -223,25 +240,37 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
             const float4* B4 = reinterpret_cast<const float4*>(sB[buf][tt]);
             const float4* C4 = reinterpret_cast<const float4*>(sC[buf][tt]);
             const float a = sa[buf][tt];
-            const float xv = sx[buf][tt][col];
-            const float u = sdt[buf][tt] * xv;
-            float part[4] = {0.f, 0.f, 0.f, 0.f};
+            const float dt = sdt[buf][tt];
+            float xv[CPT], u[CPT], part[CPT][4];
 #pragma unroll
-            for (int c = 0; c < NC; ++c) {
-                const float4 bv = B4[c * LANES + l], cv = C4[c * LANES + l];
-                s[4 * c + 0] = fmaf(a, s[4 * c + 0], bv.x * u);
-                s[4 * c + 1] = fmaf(a, s[4 * c + 1], bv.y * u);
-                s[4 * c + 2] = fmaf(a, s[4 * c + 2], bv.z * u);
-                s[4 * c + 3] = fmaf(a, s[4 * c + 3], bv.w * u);
-                part[0] = fmaf(s[4 * c + 0], cv.x, part[0]);
-                part[1] = fmaf(s[4 * c + 1], cv.y, part[1]);
-                part[2] = fmaf(s[4 * c + 2], cv.z, part[2]);
-                part[3] = fmaf(s[4 * c + 3], cv.w, part[3]);
+            for (int c = 0; c < CPT; ++c) {
+                xv[c] = sx[buf][tt][col + c];
+                u[c] = dt * xv[c];
+                part[c][0] = part[c][1] = part[c][2] = part[c][3] = 0.f;
             }
-            float sum = (part[0] + part[1]) + (part[2] + part[3]);
 #pragma unroll
-            for (int w = 1; w < LANES; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
-            if (l == 0 && j < P) y[((long long)(base + tt) * H + h) * P + j] = fmaf(dh, xv, sum);
+            for (int k = 0; k < NC; ++k) {
+                const float4 bv = B4[k * LANES + l], cv = C4[k * LANES + l];
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+                    s[c][4 * k + 0] = fmaf(a, s[c][4 * k + 0], bv.x * u[c]);
+                    s[c][4 * k + 1] = fmaf(a, s[c][4 * k + 1], bv.y * u[c]);
+                    s[c][4 * k + 2] = fmaf(a, s[c][4 * k + 2], bv.z * u[c]);
+                    s[c][4 * k + 3] = fmaf(a, s[c][4 * k + 3], bv.w * u[c]);
+                    part[c][0] = fmaf(s[c][4 * k + 0], cv.x, part[c][0]);
+                    part[c][1] = fmaf(s[c][4 * k + 1], cv.y, part[c][1]);
+                    part[c][2] = fmaf(s[c][4 * k + 2], cv.z, part[c][2]);
+                    part[c][3] = fmaf(s[c][4 * k + 3], cv.w, part[c][3]);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                float sum = (part[c][0] + part[c][1]) + (part[c][2] + part[c][3]);
+#pragma unroll
+                for (int w = 1; w < LANES; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
+                if (l == 0 && j + c < P) yp[c] = fmaf(dh, xv[c], sum);
+            }
+            yp += ystep;
         };
         if (cnt == TT) {
 #pragma unroll
@@ -253,10 +282,12 @@ ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, co
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < R; ++i) {
-        const int n = ((i >> 2) * LANES + l) * 4 + (i & 3);
-        if (n < N && j < P) Sh[(long long)n * P + j] = s[i];
-    }
+    for (int c = 0; c < CPT; ++c)
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            const int n = ((i >> 2) * LANES + l) * 4 + (i & 3);
+            if (n < N && j + c < P) Sh[(long long)n * P + j + c] = s[c][i];
+        }
 }
 
 // One block a (token, part of the row): v = y silu(z); v / rms(v) * w * scale.  A thread keeps up to eight of
@@ -337,7 +368,7 @@ UB_API int ub_ssm_scan(const float* xbc, const float* dtv, const float* dec, con
     if (n_seqs <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || P <= 0 || N <= 0 || N > 256 || H > 65535 || n_seqs > 65535) return UB_ERR_ARG;
     const int lanes = N >= 128 ? 32 : (N >= 64 ? 16 : 8);
-    const int cols = 256 / lanes;
+    const int cols = 256 / lanes * SSM_CPT;
     const dim3 grid((P + cols - 1) / cols, H, n_seqs), block(256);
     const int per = (N + lanes - 1) / lanes;               // at most 8: N <= 256
     const bool vec = N % 4 == 0 && P % 4 == 0 && (((uintptr_t)xbc) & 15) == 0;
