@@ -457,6 +457,24 @@ def test_state_space_kernels_in_one_piece_in_portions_and_in_a_batch(shape):
         assert torch.equal(o[0], whole[t])
 
 
+def test_scan_gives_the_same_bits_with_one_and_with_two_columns_a_thread():
+    """A launch with many blocks lets a thread hold two columns of the state (they share the reads of B and C); the
+    sums of a column keep their order, so forty sequences in one launch give each the bits of one sequence alone."""
+    ops = _ops()
+    H, P_, N, G, T, n = 6, 8, 16, 3, 21, 40
+    C = H * P_ + 2 * G * N
+    g = torch.Generator().manual_seed(3)
+    xbc, dtv, dec = torch.randn(T, C, generator=g), torch.rand(T, H, generator=g), torch.rand(T, H, generator=g)
+    d = torch.randn(H, generator=g).to(DEV)
+    y1, S1 = torch.empty(T, H * P_, device=DEV), torch.zeros(1, H, N, P_, device=DEV)
+    ops.ssm_scan(xbc.to(DEV), dtv.to(DEV), dec.to(DEV), d, y1, S1, _Seqs([0, T], [0]), H, P_, N, G)
+    yn, Sn = torch.empty(n * T, H * P_, device=DEV), torch.zeros(n, H, N, P_, device=DEV)
+    ops.ssm_scan(xbc.repeat(n, 1).to(DEV), dtv.repeat(n, 1).to(DEV), dec.repeat(n, 1).to(DEV), d, yn, Sn,
+                 _Seqs([i * T for i in range(n + 1)], list(range(n))), H, P_, N, G)
+    for i in (0, 17, n - 1):
+        assert torch.equal(yn[i * T:(i + 1) * T], y1) and torch.equal(Sn[i], S1[0])
+
+
 def test_the_state_keeps_an_early_input_for_hundreds_of_tokens():
     """A decay next to 1 and inputs of zero afterwards: what token 0 wrote is read out unchanged 400 tokens later."""
     ops = _ops()

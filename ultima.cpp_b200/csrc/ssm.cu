@@ -91,12 +91,12 @@ __global__ void ssm_conv_state_update_kernel(const float* __restrict__ p, SsmSha
     for (int k = 0; k < K; ++k) st[(long long)k * C + c] = tmp[k];
 }
 
-// The recurrence.  A block of 256 threads takes 256 / LANES * SSM_CPT value channels of one head of one sequence; LANES
+// The recurrence.  A block of 256 threads takes 256 / LANES * CPT value channels of one head of one sequence; LANES
 // (8, 16 or 32, by the state's size alone, so that the order of every sum is the same whatever the batch) lanes
 // hold one column of S, lane l the state channels of the float4 chunks l, l + LANES, ...: the lanes of a column
 // read consecutive bytes of shared memory in one instruction.  More lanes a column mean more warps with fewer
 // values each: the kernel is bound by the latency of a token's chain, which many warps hide.  A thread holds
-// SSM_CPT neighbouring columns, which share its reads of B and C (the kernel issues fewer instructions an element).  Tokens come through shared memory a stage at a time,
+// CPT neighbouring columns, which share its reads of B and C (the kernel issues fewer instructions an element).  Tokens come through shared memory a stage at a time,
 // the next stage asked for (cp.async) while this one is worked on.  The state's update does not wait for the
 // read-out: a token costs two operations a state element and three exchanges.
 __device__ __forceinline__ void ssm_cp4(float* dst, const float* src) {
@@ -111,23 +111,24 @@ __device__ __forceinline__ void ssm_cp16(float* dst, const float* src) {
 // Stages of tokens in shared memory: SSM_STAGES - 1 of them are on their way while one is worked on (a copy from
 // the L2 takes about as long as the arithmetic of several dozen tokens).
 constexpr int SSM_STAGES = 4;
-constexpr int SSM_CPT = 2;                                // columns of S a thread holds: they share every read of B and C
-template <int R, int LANES>
+// CPT: columns of S a thread holds (1 or 2): they share every read of B and C.  A column's sums have the same order
+// either way, so the choice (by how many blocks a launch has) changes no bit of the result.
+template <int R, int LANES, int CPT>
 struct SsmScanLayout {
-    static constexpr int NP = LANES * R, COLS = 256 / LANES * SSM_CPT;
+    static constexpr int NP = LANES * R, COLS = 256 / LANES * CPT;
     static constexpr int TT = NP <= 128 ? 16 : 8;         // tokens a stage
     static constexpr size_t BYTES = (size_t)SSM_STAGES * TT * (2 * NP + COLS + 2) * sizeof(float);
 };
 
 // VEC: N, P and the row stride are multiples of 4 and xbc starts on a 16-byte boundary: 16-byte copies.
-template <int R, int LANES, bool VEC>
+template <int R, int LANES, int CPT, bool VEC>
 __global__ void __launch_bounds__(256)
 ssm_scan_kernel(const float* __restrict__ xbc, const float* __restrict__ dtv, const float* __restrict__ dec,
                 const float* __restrict__ Dw, float* __restrict__ y, float* __restrict__ S,
                 const int* __restrict__ seq_start, const int* __restrict__ seq_slot, int H, int P, int N, int G) {
     static_assert(R % 4 == 0, "a lane holds whole float4 chunks");
-    constexpr int CPT = SSM_CPT, COLS = 256 / LANES * CPT, NP = LANES * R, NC = R / 4;
-    constexpr int TT = SsmScanLayout<R, LANES>::TT, ST = SSM_STAGES;
+    constexpr int COLS = 256 / LANES * CPT, NP = LANES * R, NC = R / 4;
+    constexpr int TT = SsmScanLayout<R, LANES, CPT>::TT, ST = SSM_STAGES;
     extern __shared__ __align__(16) float smem[];
     float (*sB)[TT][NP] = reinterpret_cast<float (*)[TT][NP]>(smem);                       // [ST][TT][NP]
     float (*sC)[TT][NP] = reinterpret_cast<float (*)[TT][NP]>(smem + ST * TT * NP);
@@ -364,31 +365,38 @@ UB_API int ub_ssm_conv_state_update(const float* p, long long ldp, int n_parts, 
 }
 
 UB_API int ub_ssm_scan(const float* xbc, const float* dtv, const float* dec, const float* Dw, float* y, float* S,
-                       const int* seq_start, const int* seq_slot, int n_seqs, int H, int P, int N, int G, cudaStream_t st) {
+                       const int* seq_start, const int* seq_slot, int n_seqs, int H, int P, int N, int G, int sm_count,
+                       cudaStream_t st) {
     if (n_seqs <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || P <= 0 || N <= 0 || N > 256 || H > 65535 || n_seqs > 65535) return UB_ERR_ARG;
     const int lanes = N >= 128 ? 32 : (N >= 64 ? 16 : 8);
-    const int cols = 256 / lanes * SSM_CPT;
+    // two columns a thread where that still leaves about one and a half blocks for every multiprocessor (measured at
+    // 2,048 tokens, state 128, heads of 64: 64 heads 875 -> 681 us with two, 32 heads 568 -> 591 us)
+    const long long blocks2 = (long long)((P + 256 / lanes * 2 - 1) / (256 / lanes * 2)) * H * n_seqs;
+    const int cpt = blocks2 * 2 >= 3LL * (sm_count > 0 ? sm_count : 148) ? 2 : 1;
+    const int cols = 256 / lanes * cpt;
     const dim3 grid((P + cols - 1) / cols, H, n_seqs), block(256);
     const int per = (N + lanes - 1) / lanes;               // at most 8: N <= 256
     const bool vec = N % 4 == 0 && P % 4 == 0 && (((uintptr_t)xbc) & 15) == 0;
     cudaError_t e;
-#define GO3(RR, LL, VV) do { \
-        constexpr size_t smem = SsmScanLayout<RR, LL>::BYTES; \
+#define GO4(RR, LL, CC, VV) do { \
+        constexpr size_t smem = SsmScanLayout<RR, LL, CC>::BYTES; \
         static bool attr_done = false; \
         if (!attr_done) { \
-            e = cudaFuncSetAttribute(ssm_scan_kernel<RR, LL, VV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            e = cudaFuncSetAttribute(ssm_scan_kernel<RR, LL, CC, VV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) return (int)e; \
             attr_done = true; \
         } \
-        e = ub_launch_dependent(ssm_scan_kernel<RR, LL, VV>, grid, block, smem, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G); \
+        e = ub_launch_dependent(ssm_scan_kernel<RR, LL, CC, VV>, grid, block, smem, st, xbc, dtv, dec, Dw, y, S, seq_start, seq_slot, H, P, N, G); \
     } while (0)
-#define GO2(RR, LL) do { if (vec) GO3(RR, LL, true); else GO3(RR, LL, false); } while (0)
+#define GO3(RR, LL, CC) do { if (vec) GO4(RR, LL, CC, true); else GO4(RR, LL, CC, false); } while (0)
+#define GO2(RR, LL) do { if (cpt == 2) GO3(RR, LL, 2); else GO3(RR, LL, 1); } while (0)
 #define GO(RR) do { if (lanes == 32) GO2(RR, 32); else if (lanes == 16) GO2(RR, 16); else GO2(RR, 8); } while (0)
     if (per <= 4) GO(4); else GO(8);
+#undef GO
 #undef GO2
 #undef GO3
-#undef GO
+#undef GO4
     return (int)e;
 }
 
